@@ -1,0 +1,200 @@
+// C ABI of libfhob.so: argument validation, the row-statistics pre-pass and
+// dispatch of the four recomputation passes to the tensor-core or CUDA-core
+// kernels.  Host wrapper role of flash_bwdbwd in the reference
+// (fhog/triton_bwdbwd.py:557-648).
+#include <cstdio>
+#include <cstring>
+
+#include "fhob_common.cuh"
+
+namespace fhob {
+
+namespace {
+thread_local char g_cuda_error[512] = "";
+}
+
+void set_cuda_error(cudaError_t e, const char* where) {
+  std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e),
+                cudaGetErrorString(e));
+}
+void set_cuda_error_text(const char* text) { std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s", text); }
+
+namespace {
+
+// One warp per query row: D = sum_d dO*O, then the two folded vectors.
+// Block 0 also clears the status word, so every operator call starts clean.
+template <typename T>
+__global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
+                               float* __restrict__ nlc, float* __restrict__ nds, int* status, long rows, int d,
+                               float scale) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+  long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  const T* po = o + row * d;
+  const T* pd = d_o + row * d;
+  float acc = 0.f;
+  for (int c = lane; c < d; c += 32) acc = fmaf(static_cast<float>(po[c]), static_cast<float>(pd[c]), acc);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    nds[row] = -acc * scale;
+    nlc[row] = -lse[row] * kLog2e;
+  }
+}
+
+__global__ void row_stats_kernel(const float* nds, const float* ndd, const float* nbs, float* d_out, float* dd_out,
+                                 float* b_out, long rows, float inv_scale) {
+  long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  if (d_out) d_out[i] = -nds[i] * inv_scale;
+  if (dd_out) dd_out[i] = -ndd[i];
+  if (b_out) b_out[i] = -nbs[i] * inv_scale;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate(const FhobProblem* p, bool need_outputs) {
+  if (!p) return FHOB_ERR_ARG;
+  if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0) return FHOB_ERR_ARG;
+  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
+  if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
+  if (p->causal != 0 && p->causal != 1) return FHOB_ERR_ARG;
+  const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->ddq, p->ddk, p->ddv, p->lse};
+  for (const void* x : ins) {
+    if (!x) return FHOB_ERR_ARG;
+    if (!aligned16(x)) return FHOB_ERR_ALIGN;
+  }
+  if (need_outputs) {
+    const void* outs[] = {p->dq2, p->dk2, p->dv2, p->ddo};
+    for (const void* x : outs) {
+      if (!x) return FHOB_ERR_ARG;
+      if (!aligned16(x)) return FHOB_ERR_ALIGN;
+    }
+  }
+  size_t row_bytes = static_cast<size_t>(p->d) * (p->dtype == FHOB_BF16 ? 2 : 4);
+  if (row_bytes % 16 != 0) return FHOB_ERR_SHAPE;  // rows must stay 16-byte aligned
+  if (p->d > 128) return FHOB_ERR_SHAPE;
+  if (!p->workspace || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) return FHOB_ERR_WORKSPACE;
+  if (p->workspace_bytes < fhob_workspace_bytes(p->bh, p->n_q)) return FHOB_ERR_WORKSPACE;
+  if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) return FHOB_ERR_SHAPE;
+  return FHOB_OK;
+}
+
+bool use_tc(const FhobProblem& p) {
+  if (p.impl == FHOB_IMPL_SIMT) return false;
+  if (p.impl == FHOB_IMPL_TCGEN05) return true;
+  return tc_supported(p);
+}
+
+int run_pass(int pass, const FhobProblem* p, void* stream) {
+  int st = validate(p, pass >= 3);
+  if (st != FHOB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return use_tc(*p) ? tc_pass(pass, *p, s) : simt_pass(pass, *p, s);
+}
+
+}  // namespace
+}  // namespace fhob
+
+using namespace fhob;
+
+extern "C" {
+
+int fhob_version(void) { return 100; }
+
+const char* fhob_strerror(int status) {
+  switch (status) {
+    case FHOB_OK: return "ok";
+    case FHOB_ERR_ARG: return "invalid argument (null pointer, bad dtype/impl/causal flag or non-positive size)";
+    case FHOB_ERR_SHAPE: return "shape not supported (head dim must keep rows 16-byte aligned and be <= 128; "
+                                "the tensor-core kernels need bf16 and d in {64,128})";
+    case FHOB_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
+    case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes()";
+    case FHOB_ERR_CUDA: return "a CUDA call failed (see fhob_last_cuda_error)";
+    case FHOB_ERR_ARCH: return "the tensor-core kernels need a compute capability 10.x device";
+    default: break;
+  }
+  if (status & FHOB_ERR_TIMEOUT) return "device: a bounded wait ran out of iterations (results are invalid)";
+  if (status & FHOB_ERR_SMEM_ALIGN) return "device: shared memory base not 1024-byte aligned";
+  return "unknown status";
+}
+
+const char* fhob_last_cuda_error(void) { return g_cuda_error; }
+
+size_t fhob_workspace_bytes(int32_t bh, int32_t n_q) {
+  if (bh <= 0 || n_q <= 0) return 0;
+  size_t rows = static_cast<size_t>(bh) * static_cast<size_t>(n_q);
+  // the tail pad lets the key-tiled pass read whole 64-query groups of the last head
+  return kWorkspaceHeaderBytes + 4 * rows * sizeof(float) + kWorkspaceTailBytes;
+}
+
+int fhob_prepass(const FhobProblem* p, void* stream) {
+  int st = validate(p, false);
+  if (st != FHOB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  RowVectors rv = row_vectors(*p);
+  long rows = static_cast<long>(p->bh) * p->n_q;
+  const int warps = 8;
+  unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  if (p->dtype == FHOB_BF16) {
+    prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.nds,
+        rv.status, rows, p->d, p->scale);
+  } else {
+    prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
+                                                      static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.nds,
+                                                      rv.status, rows, p->d, p->scale);
+  }
+  FHOB_CUDA_OK(cudaGetLastError());
+  return FHOB_OK;
+}
+
+int fhob_pass1(const FhobProblem* p, void* stream) { return run_pass(1, p, stream); }
+int fhob_pass2(const FhobProblem* p, void* stream) { return run_pass(2, p, stream); }
+int fhob_pass3(const FhobProblem* p, void* stream) { return run_pass(3, p, stream); }
+int fhob_pass4(const FhobProblem* p, void* stream) { return run_pass(4, p, stream); }
+
+int fhob_bwdbwd(const FhobProblem* p, void* stream) {
+  int st = validate(p, true);
+  if (st != FHOB_OK) return st;
+  st = fhob_prepass(p, stream);
+  if (st != FHOB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc = use_tc(*p);
+  for (int pass = 1; pass <= 4; ++pass) {
+    st = tc ? tc_pass(pass, *p, s) : simt_pass(pass, *p, s);
+    if (st != FHOB_OK) return st;
+  }
+  return FHOB_OK;
+}
+
+int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_out, void* stream) {
+  int st = validate(p, false);
+  if (st != FHOB_OK) return st;
+  RowVectors rv = row_vectors(*p);
+  long rows = static_cast<long>(p->bh) * p->n_q;
+  unsigned grid = static_cast<unsigned>((rows + 255) / 256);
+  row_stats_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(rv.nds, rv.ndd, rv.nbs, d_out, dd_out, b_out,
+                                                                        rows, 1.f / p->scale);
+  FHOB_CUDA_OK(cudaGetLastError());
+  return FHOB_OK;
+}
+
+int fhob_read_status(const FhobProblem* p, void* stream) {
+  if (!p || !p->workspace) return FHOB_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int host = 0;
+  FHOB_CUDA_OK(cudaMemcpyAsync(&host, p->workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  FHOB_CUDA_OK(cudaStreamSynchronize(s));
+  return host;
+}
+
+int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !o_out || !lse_out) return FHOB_ERR_ARG;
+  if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
+  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
+  return simt_forward(*p, o_out, lse_out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,72 @@
+// Shared definitions of the double-backward attention kernels.
+//
+// Notation (reference: fhog/triton_bwdbwd.py:178-313, jax_refs/flash_impl.py:176-229):
+//   S   = Q K^T * scale            P   = exp(S - L)
+//   A2  = ddQ K^T + Q ddK^T        ddS = scale * A2
+//   dP  = dO V^T                   X   = dO ddV^T
+//   D_i = sum_d dO O               dd_i = sum_j ddS P
+//   dP2 = X + dP (ddS - dd) - D ddS      b_i = sum_j dP2 P
+//   dS  = scale P (dP - D)         dS2 = scale P (dP2 - b)     ddP = P (ddS - dd)
+//   dQ2 = dS ddK + dS2 K           ddO = ddP V + P ddV
+//   dK2 = dS^T ddQ + dS2^T Q       dV2 = ddP^T dO
+//
+// The four row vectors are staged in the workspace with sign and scale folded
+// in, so the per-element work is FMAs only:
+//   nlc = -L*log2(e)   nds = -D*scale   ndd = -dd   nbs = -b*scale
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fhob.h"
+
+namespace fhob {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kWorkspaceHeaderBytes = 256;
+constexpr int kWorkspaceTailBytes = 1024;
+
+struct RowVectors {
+  int* status;  // device status word (workspace header)
+  float* nlc;   // -L * log2(e)
+  float* nds;   // -D * scale
+  float* ndd;   // -dd
+  float* nbs;   // -b * scale
+};
+
+inline RowVectors row_vectors(const FhobProblem& p) {
+  RowVectors r;
+  char* base = static_cast<char*>(p.workspace);
+  size_t n = static_cast<size_t>(p.bh) * static_cast<size_t>(p.n_q);
+  r.status = reinterpret_cast<int*>(base);
+  float* f = reinterpret_cast<float*>(base + kWorkspaceHeaderBytes);
+  r.nlc = f;
+  r.nds = f + n;
+  r.ndd = f + 2 * n;
+  r.nbs = f + 3 * n;
+  return r;
+}
+
+// Per-thread record of the last CUDA error (read through fhob_last_cuda_error).
+void set_cuda_error(cudaError_t e, const char* where);
+void set_cuda_error_text(const char* text);
+
+#define FHOB_CUDA_OK(expr)                                  \
+  do {                                                      \
+    cudaError_t e__ = (expr);                               \
+    if (e__ != cudaSuccess) {                               \
+      ::fhob::set_cuda_error(e__, #expr);                   \
+      return FHOB_ERR_CUDA;                                 \
+    }                                                       \
+  } while (0)
+
+// CUDA-core kernels (fp32 accumulate, any sizes): simt_kernels.cu
+int simt_pass(int pass, const FhobProblem& p, cudaStream_t s);
+int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s);
+
+// tcgen05 / TMEM / TMA kernels (bf16, d in {64,128}): tc_kernels.cu
+bool tc_supported(const FhobProblem& p);
+int tc_pass(int pass, const FhobProblem& p, cudaStream_t s);
+
+}  // namespace fhob

@@ -1,0 +1,209 @@
+"""Host side of the B200 double-backward flash attention operator.
+
+Mirrors the reference entry point
+``flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale) -> (dQ2, dK2, dV2, ddO)``
+(fhog/triton_bwdbwd.py:557-648) on top of the C ABI of libfhob.so.  torch is
+used for device memory and streams only; all arithmetic runs in the library's
+CUDA kernels, and a missing library is an error rather than a fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _fold(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dim() == 4:
+        t = t.reshape(t.shape[0] * t.shape[1], t.shape[2], t.shape[3])
+    if t.dim() != 3:
+        raise ValueError(f"{name}: expected (BH, N, D) or (B, H, N, D), got {tuple(t.shape)}")
+    return t.contiguous()
+
+
+class _Problem:
+    """Validated tensors + the FhobProblem struct that points at them."""
+
+    def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True):
+        names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
+        tensors = [Q, K, V, O, dO, ddQ, ddK, ddV]
+        if impl not in _lib.IMPL:
+            raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
+        for n, t in zip(names, tensors):
+            if not isinstance(t, torch.Tensor):
+                raise TypeError(f"{n} must be a torch.Tensor")
+        dev, dt = Q.device, Q.dtype
+        if dev.type != "cuda":
+            raise ValueError("device tensors expected (use flash_bwdbwd, which stages host tensors)")
+        if dt not in (torch.bfloat16, torch.float32):
+            raise TypeError(f"dtype {dt} not supported: bfloat16 or float32")
+        for n, t in zip(names, tensors):
+            if t.device != dev:
+                raise ValueError(f"{n} is on {t.device}, Q is on {dev}")
+            if t.dtype != dt:
+                raise TypeError(f"{n} has dtype {t.dtype}, Q has {dt}")
+        self.out_shape_q, self.out_shape_k = Q.shape, K.shape
+        t3 = [_fold(t, n) for n, t in zip(names, tensors)]
+        q, k, v, o, do, ddq, ddk, ddv = t3
+        bh, n_q, d = q.shape
+        n_k = k.shape[1]
+        for n, t in zip(names, t3):
+            want = (bh, n_q, d) if n in ("Q", "O", "dO", "ddQ") else (bh, n_k, d)
+            if tuple(t.shape) != want:
+                raise ValueError(f"{n}: shape {tuple(t.shape)} does not match {want}")
+        lse = L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)
+        if tuple(lse.shape) != (bh, n_q) or L.device != dev:
+            raise ValueError(f"L: expected {(bh, n_q)} on {dev}, got {tuple(L.shape)} on {L.device}")
+        lse = lse.to(torch.float32).contiguous()
+        self.keep = t3 + [lse]
+        self.device = dev
+        self.stream = torch.cuda.current_stream(dev).cuda_stream
+        lib = _lib.load()
+        nbytes = lib.fhob_workspace_bytes(bh, n_q)
+        self.ws = _workspace(dev, self.stream, nbytes)
+        p = _lib.FhobProblem()
+        p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
+        p.dtype = _lib.FHOB_BF16 if dt == torch.bfloat16 else _lib.FHOB_F32
+        p.causal = 1 if is_causal else 0
+        p.impl = _lib.IMPL[impl]
+        p.scale = float(scale)
+        p.q, p.k, p.v, p.o, p.d_o = (t.data_ptr() for t in (q, k, v, o, do))
+        p.ddq, p.ddk, p.ddv, p.lse = (t.data_ptr() for t in (ddq, ddk, ddv, lse))
+        if need_outputs:
+            self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(q)
+            self.dk2, self.dv2 = torch.empty_like(k), torch.empty_like(k)
+            p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
+        p.workspace, p.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
+        self.p = p
+        self.bh, self.n_q = bh, n_q
+
+    def outputs(self):
+        return (self.dq2.reshape(self.out_shape_q), self.dk2.reshape(self.out_shape_k),
+                self.dv2.reshape(self.out_shape_k), self.ddo.reshape(self.out_shape_q))
+
+    def status(self) -> int:
+        """Synchronises the stream and returns the device status word."""
+        return _lib.load().fhob_read_status(C.byref(self.p), C.c_void_p(self.stream))
+
+
+def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check):
+    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl)
+    lib = _lib.load()
+    with torch.cuda.device(prob.device):
+        _lib.check(lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream)), "fhob_bwdbwd")
+        if check:
+            _lib.check(prob.status(), "fhob_bwdbwd (device status)")
+    return prob.outputs()
+
+
+def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = False,
+                 impl: str = "auto", check: bool = False,
+                 device: Optional[torch.device] = None) -> Tuple[torch.Tensor, ...]:
+    """Double backward of scaled-dot-product attention.
+
+    Same positional signature and return order as the reference
+    (fhog/triton_bwdbwd.py:558, :648).  Tensors are ``(BH, N, D)`` like the
+    reference or ``(B, H, N, D)``; bfloat16 (tensor-core kernels, fp32
+    accumulation) or float32 (CUDA-core kernels).  ``L`` is the logsumexp of
+    the masked scaled scores, any float dtype (used as fp32).
+
+    Keyword-only additions, all behaviour-preserving by default:
+    ``is_causal`` bottom-right aligned causal mask (the reference operator has
+    none; its oracle does: jax_refs/flash_impl.py:86-91); ``impl`` one of
+    "auto", "simt", "tcgen05"; ``check`` synchronise and raise if a device
+    wait timed out.
+
+    Host (CPU) tensors are accepted too: they are staged to ``device``
+    (default: current CUDA device) on the current stream, preferably from
+    pinned memory, and the four results come back as pinned host tensors after
+    a stream synchronise.
+    """
+    if Q.device.type == "cuda":
+        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check)
+    if not torch.cuda.is_available():
+        raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    staged = [t.to(dev, non_blocking=True) for t in (Q, K, V, O, dO, ddQ, ddK, ddV, L)]
+    outs = _run_device(*staged, scale, is_causal, impl, check)
+    host = [torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True) for o in outs]
+    for h, o in zip(host, outs):
+        h.copy_(o, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    return tuple(host)
+
+
+def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False):
+    """O(N)-memory producer of the saved forward results: returns ``(O, L)``.
+
+    ``O = softmax(Q K^T scale) V`` in the input dtype and the fp32 logsumexp
+    ``L`` — the two tensors ``flash_bwdbwd`` consumes.  Role of the reference's
+    forward kernel and ``produce_L`` (fhog/triton_flash.py:12-133, :252-258),
+    which is dense, returns L in the input dtype and raises for causal masks.
+    """
+    shape_q = Q.shape
+    q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
+    if q.device.type != "cuda" or q.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("attention_forward needs CUDA bfloat16/float32 tensors")
+    bh, n_q, d = q.shape
+    if scale is None:
+        scale = d ** -0.5
+    o = torch.empty_like(q)
+    lse = torch.empty(bh, n_q, dtype=torch.float32, device=q.device)
+    p = _lib.FhobProblem()
+    p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
+    p.dtype = _lib.FHOB_BF16 if q.dtype == torch.bfloat16 else _lib.FHOB_F32
+    p.causal, p.impl, p.scale = (1 if is_causal else 0), 0, float(scale)
+    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().fhob_forward(C.byref(p), C.c_void_p(o.data_ptr()), C.c_void_p(lse.data_ptr()),
+                                            C.c_void_p(stream)), "fhob_forward")
+    return o.reshape(shape_q), lse.reshape(shape_q[:-1])
+
+
+def produce_L(Q, K, is_causal: bool = False, scale=None):
+    """fp32 logsumexp of the scaled scores, same name and argument order as the
+    reference helper (fhog/triton_flash.py:252-258) but O(N) memory, fp32 and
+    causal-capable."""
+    return attention_forward(Q, K, K, scale, is_causal=is_causal)[1]
+
+
+def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl="auto", upto=4):
+    """Runs the pre-pass and passes 1..``upto`` one by one (unit tests, profiling).
+
+    Returns a dict with the row statistics ``d``, ``dd``, ``b`` (fp32, (BH, N_Q));
+    entries a pass has not produced yet are garbage), the outputs produced so
+    far, and the device ``status`` word.
+    """
+    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl)
+    lib = _lib.load()
+    s = C.c_void_p(prob.stream)
+    with torch.cuda.device(prob.device):
+        _lib.check(lib.fhob_prepass(C.byref(prob.p), s), "fhob_prepass")
+        for i in range(1, upto + 1):
+            _lib.check(getattr(lib, f"fhob_pass{i}")(C.byref(prob.p), s), f"fhob_pass{i}")
+        vecs = torch.empty(3, prob.bh, prob.n_q, dtype=torch.float32, device=prob.device)
+        _lib.check(lib.fhob_row_stats(C.byref(prob.p), C.c_void_p(vecs[0].data_ptr()),
+                                      C.c_void_p(vecs[1].data_ptr()), C.c_void_p(vecs[2].data_ptr()), s),
+                   "fhob_row_stats")
+        status = prob.status()
+    out = dict(d=vecs[0], dd=vecs[1], b=vecs[2], status=status)
+    if upto >= 3:
+        out["dq2"], out["ddo"] = prob.dq2, prob.ddo
+    if upto >= 4:
+        out["dk2"], out["dv2"] = prob.dk2, prob.dv2
+    return out

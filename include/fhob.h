@@ -1,0 +1,156 @@
+/*
+ * fhob.h — C ABI of the B200 double-backward flash attention library (libfhob.so).
+ *
+ * The library replaces one operator of the reference project: the double
+ * backward of scaled-dot-product attention,
+ *
+ *     flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale) -> (dQ2, dK2, dV2, ddO)
+ *
+ * (reference: fhog/triton_bwdbwd.py:557-648, exported at fhog/__init__.py:1-3).
+ * Every entry point takes plain device pointers and sizes, launches on the
+ * CUDA stream it is given and returns an int status (0 = ok).  No entry point
+ * allocates device memory unless its comment says so; scratch is a caller
+ * provided workspace of fhob_workspace_bytes() bytes.
+ *
+ * Layout: every matrix is row-major (BH, N, D) with the batch and head axes
+ * folded into BH like the reference does (fhog/triton_bwdbwd.py:577), rows
+ * contiguous and 16-byte aligned.  L is fp32 (BH, N_Q).
+ */
+#ifndef FHOB_H_
+#define FHOB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element types of the eleven matrices (all share one type). */
+enum { FHOB_BF16 = 0, FHOB_F32 = 1 };
+
+/* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for bf16,
+ * fp32 CUDA-core kernels for fp32.  SIMT forces the CUDA-core kernels for
+ * either type (debugging aid; same four passes, same row statistics). */
+enum { FHOB_IMPL_AUTO = 0, FHOB_IMPL_SIMT = 1, FHOB_IMPL_TCGEN05 = 2 };
+
+/* Status codes.  Device-side conditions are accumulated (OR-ed) into the
+ * status word at the start of the workspace and fetched with
+ * fhob_read_status(). */
+enum {
+  FHOB_OK = 0,
+  FHOB_ERR_ARG = 1,        /* null pointer, bad dtype/impl, non-positive size */
+  FHOB_ERR_SHAPE = 2,      /* head dim / sequence length not supported by the chosen kernels */
+  FHOB_ERR_ALIGN = 3,      /* a pointer is not 16-byte aligned */
+  FHOB_ERR_WORKSPACE = 4,  /* workspace missing or too small */
+  FHOB_ERR_CUDA = 5,       /* a CUDA runtime/driver call failed (see fhob_last_cuda_error) */
+  FHOB_ERR_ARCH = 6,       /* tensor-core kernels need compute capability 10.x */
+  FHOB_ERR_TIMEOUT = 64,   /* device: a bounded mbarrier wait ran out (bit in the status word) */
+  FHOB_ERR_SMEM_ALIGN = 128 /* device: dynamic shared memory base was not 1024-byte aligned */
+};
+
+/*
+ * One double-backward problem.  Replaces the argument list of
+ * flash_bwdbwd (fhog/triton_bwdbwd.py:558) and of its two kernel launches
+ * (fhog/triton_bwdbwd.py:586-612, :620-646).
+ */
+typedef struct FhobProblem {
+  int32_t bh;      /* folded batch*heads */
+  int32_t n_q;     /* query rows per head */
+  int32_t n_k;     /* key rows per head */
+  int32_t d;       /* head dim, shared by q/k and v like the reference (:577) */
+  int32_t dtype;   /* FHOB_BF16 or FHOB_F32 */
+  int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j */
+  int32_t impl;    /* FHOB_IMPL_* */
+  float scale;     /* softmax scale */
+  /* inputs, device pointers */
+  const void* q;   /* (bh, n_q, d) */
+  const void* k;   /* (bh, n_k, d) */
+  const void* v;   /* (bh, n_k, d) */
+  const void* o;   /* (bh, n_q, d) forward output */
+  const void* d_o; /* (bh, n_q, d) cotangent of o in the first backward */
+  const void* ddq; /* (bh, n_q, d) cotangent of dQ */
+  const void* ddk; /* (bh, n_k, d) cotangent of dK */
+  const void* ddv; /* (bh, n_k, d) cotangent of dV */
+  const float* lse; /* (bh, n_q) fp32 logsumexp of the masked scaled scores */
+  /* outputs, device pointers, same element type as the inputs */
+  void* dq2; /* (bh, n_q, d) */
+  void* dk2; /* (bh, n_k, d) */
+  void* dv2; /* (bh, n_k, d) */
+  void* ddo; /* (bh, n_q, d) */
+  /* scratch: fhob_workspace_bytes(bh, n_q) bytes, 256-byte aligned */
+  void* workspace;
+  size_t workspace_bytes;
+} FhobProblem;
+
+/* Library version (major*10000 + minor*100 + patch). */
+int fhob_version(void);
+
+/* Text for a status code. */
+const char* fhob_strerror(int status);
+
+/* Text of the last CUDA error this thread's calls ran into ("" if none). */
+const char* fhob_last_cuda_error(void);
+
+/*
+ * Bytes of scratch one problem needs: a 256-byte header holding the device
+ * status word plus four fp32 row vectors of bh*n_q entries (-L*log2e,
+ * -D*scale, -dd, -b*scale).  This is the whole extra memory of the operator —
+ * linear in n_q.  Replaces the reference's D, dD and B temporaries
+ * (fhog/triton_bwdbwd.py:580-584).
+ */
+size_t fhob_workspace_bytes(int32_t bh, int32_t n_q);
+
+/*
+ * The whole operator: row-statistics pre-pass and the four recomputation
+ * passes, queued on `stream` (a cudaStream_t) without synchronising.
+ * Replaces flash_bwdbwd (fhog/triton_bwdbwd.py:557-648).
+ */
+int fhob_bwdbwd(const FhobProblem* p, void* stream);
+
+/*
+ * The single stages, for unit tests and profiling.  They must run in this
+ * order on one stream because each consumes row vectors the previous wrote.
+ *
+ * fhob_prepass: clears the status word, D_i = sum_d dO*O (reference :580),
+ *               stores -D*scale and -L*log2(e).
+ * fhob_pass1:   dd_i = sum_j ddS_ij P_ij                 (reference :178-215)
+ * fhob_pass2:   b_i  = sum_j dP2_ij P_ij                 (reference :217-255)
+ * fhob_pass3:   dQ2 and ddO                              (reference :257-313)
+ * fhob_pass4:   dK2 and dV2, key-tiled                   (reference :321-535)
+ */
+int fhob_prepass(const FhobProblem* p, void* stream);
+int fhob_pass1(const FhobProblem* p, void* stream);
+int fhob_pass2(const FhobProblem* p, void* stream);
+int fhob_pass3(const FhobProblem* p, void* stream);
+int fhob_pass4(const FhobProblem* p, void* stream);
+
+/*
+ * Copies the row statistics out of the workspace into caller device buffers
+ * of bh*n_q floats each, undoing the internal sign/scale folding:
+ * d_out = D, dd_out = dd, b_out = b.  Any of the three may be NULL.
+ * (The reference keeps these as the tensors D, dD, B: :580-584.)
+ */
+int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_out, void* stream);
+
+/*
+ * Synchronises `stream`, reads the device status word of the workspace and
+ * returns it (0 = every bounded wait completed).  The reference has no
+ * counterpart; its kernels cannot time out.
+ */
+int fhob_read_status(const FhobProblem* p, void* stream);
+
+/*
+ * O(N)-memory producer of the two saved forward results the operator
+ * consumes: O = softmax(QK^T scale) V in the input element type and the fp32
+ * logsumexp L.  Role of flash_kernel / produce_L in the reference
+ * (fhog/triton_flash.py:12-133, :252-258), which is dense, rounds L to the
+ * input type and refuses causal masks.  Uses p->q, k, v, scale, causal;
+ * writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).  CUDA-core kernel.
+ */
+int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FHOB_H_ */

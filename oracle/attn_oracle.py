@@ -158,3 +158,47 @@ def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
     """max|x - ref| / max|ref| — the error metric every parity test uses."""
     ref = ref.double()
     return float((x.double().cpu() - ref.cpu()).abs().max() / ref.abs().max().clamp_min(1e-300))
+
+
+def bwdbwd_closed_form_chunked(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, chunk=1024):
+    """Form B evaluated over query-row chunks so that no (N_Q, N_K) matrix is
+    ever held whole: memory is O(chunk * N_K).  Same equations as
+    ``bwdbwd_closed_form``; works on any device/dtype torch supports (the
+    large-shape parity tests run it in fp64 on the GPU).  2-D per-head inputs.
+    Returns (dq2, dk2, dv2, ddo, lse, o) — the last two are the saved forward
+    results the operator consumes, produced on the way.
+    """
+    nq, nk = q.shape[-2], k.shape[-2]
+    off = nk - nq
+    dq2 = torch.empty_like(q)
+    ddo = torch.empty_like(q)
+    o = torch.empty_like(q)
+    lse = torch.empty(nq, dtype=q.dtype, device=q.device)
+    dk2 = torch.zeros_like(k)
+    dv2 = torch.zeros_like(k)
+    kj = torch.arange(nk, device=q.device)[None, :]
+    for r0 in range(0, nq, chunk):
+        r1 = min(nq, r0 + chunk)
+        qc, doc, ddqc = q[r0:r1], do[r0:r1], ddq[r0:r1]
+        s = (qc @ k.T) * scale
+        if is_causal:
+            qi = torch.arange(r0, r1, device=q.device)[:, None] + off
+            s = torch.where(qi >= kj, s, torch.full_like(s, -math.inf))
+        l = torch.logsumexp(s, dim=-1)
+        p = torch.exp(s - l[:, None])
+        lse[r0:r1] = l
+        o[r0:r1] = p @ v
+        dp = doc @ v.T
+        dds = scale * (ddqc @ k.T + qc @ ddk.T)
+        d = (p * dp).sum(-1, keepdim=True)
+        dd = (dds * p).sum(-1, keepdim=True)
+        dp2 = doc @ ddv.T - dp * dd - dds * d + dp * dds
+        ddp = p * (dds - dd)
+        b = (dp2 * p).sum(-1, keepdim=True)
+        ds2 = scale * p * (dp2 - b)
+        ds = scale * p * (dp - d)
+        dq2[r0:r1] = ds @ ddk + ds2 @ k
+        ddo[r0:r1] = p @ ddv + ddp @ v
+        dk2 += ds.T @ ddqc + ds2.T @ qc
+        dv2 += ddp.T @ doc
+    return dq2, dk2, dv2, ddo, lse, o

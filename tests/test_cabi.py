@@ -1,0 +1,97 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the
+header declares, and rejects bad problems before touching a GPU."""
+from __future__ import annotations
+
+import ctypes as C
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from fhob import _lib
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("fhob_build", ROOT / "flash-hob_b200" / "build.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+    return _lib.load()
+
+
+def test_exports_every_declared_symbol(lib):
+    header = (ROOT / "include" / "fhob.h").read_text()
+    declared = set(re.findall(r"\b(fhob_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_lib.SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert lib.fhob_version() >= 100
+
+
+def test_struct_matches_header(lib):
+    header = (ROOT / "include" / "fhob.h").read_text()
+    body = header.split("typedef struct FhobProblem {")[1].split("} FhobProblem;")[0]
+    fields = re.findall(r"^\s*(?:const\s+)?[a-z0-9_]+\*?\s+\*?([a-z0-9_]+);", body, flags=re.M)
+    assert fields == [f[0] for f in _lib.FhobProblem._fields_]
+
+
+def test_workspace_is_linear_in_rows(lib):
+    w1 = lib.fhob_workspace_bytes(4, 1024)
+    w2 = lib.fhob_workspace_bytes(4, 2048)
+    w4 = lib.fhob_workspace_bytes(4, 4096)
+    assert w2 - w1 == 4 * 1024 * 16 and w4 - w2 == 4 * 2048 * 16   # 4 fp32 row vectors
+    assert lib.fhob_workspace_bytes(0, 5) == 0
+
+
+def _problem(**over):
+    """A well-formed problem over fake (never dereferenced) 256-byte aligned addresses."""
+    p = _lib.FhobProblem()
+    p.bh, p.n_q, p.n_k, p.d = 2, 128, 256, 64
+    p.dtype, p.causal, p.impl, p.scale = _lib.FHOB_BF16, 0, 0, 0.125
+    for i, name in enumerate(("q", "k", "v", "o", "d_o", "ddq", "ddk", "ddv", "lse", "dq2", "dk2", "dv2", "ddo")):
+        setattr(p, name, 0x10000 + 0x1000 * i)
+    p.workspace, p.workspace_bytes = 0x100000, 1 << 20
+    for k, v in over.items():
+        setattr(p, k, v)
+    return p
+
+
+@pytest.mark.parametrize("over,code", [
+    (dict(q=None), 1), (dict(lse=None), 1), (dict(dq2=None), 1), (dict(bh=0), 1), (dict(dtype=7), 1),
+    (dict(impl=9), 1), (dict(causal=2), 1),
+    (dict(d=129), 2), (dict(d=4), 2), (dict(d=256), 2),
+    (dict(impl=2, dtype=1), 2), (dict(impl=2, d=32), 2),
+    (dict(k=0x10008), 3), (dict(ddo=0x20004), 3),
+    (dict(workspace=None), 4), (dict(workspace_bytes=100), 4), (dict(workspace=0x100010), 4),
+])
+def test_bad_problems_are_rejected_before_launch(lib, over, code):
+    p = _problem(**over)
+    assert lib.fhob_bwdbwd(C.byref(p), None) == code
+    assert lib.fhob_strerror(code) != b"unknown status"
+
+
+def test_null_problem(lib):
+    assert lib.fhob_bwdbwd(None, None) == 1
+    assert lib.fhob_pass3(None, None) == 1
+
+
+def test_host_wrapper_validation():
+    import fhob
+    q = torch.zeros(2, 128, 64)
+    with pytest.raises((RuntimeError, ValueError)):
+        fhob.flash_bwdbwd(q, q, q, q, q, q, q, q, torch.zeros(2, 128), 0.125)  # CPU tensors, no GPU here
+    if not torch.cuda.is_available():
+        with pytest.raises(ValueError):
+            fhob.ops._Problem(q, q, q, q, q, q, q, q, torch.zeros(2, 128), 0.125, False, "auto")
+        with pytest.raises(ValueError):
+            fhob.ops._Problem(q, q, q, q, q, q, q, q, torch.zeros(2, 128), 0.125, False, "fast")
+
+
+def test_missing_library_is_loud(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libfhob.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        _lib.load()
