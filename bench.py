@@ -1,0 +1,319 @@
+#!/usr/bin/env python
+"""Benchmark of the double-backward flash attention operator.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl fhob|reference]
+
+One "step" is one call of the operator (pre-pass + four passes) over one batch
+of synthetic heads resident in HBM.  Work is sharded over batch x heads with no
+collective (weak scaling: every GPU gets the same number of heads), so under
+torchrun each rank runs its own shard and the only communication is the
+barrier/max-reduction around the timed region.  Rank 0 prints ONE JSON line.
+
+Flop accounting: F_alg = 24*BH*pairs*D (the 12 distinct contractions of the
+maths) is what `value`, `e2e` and `cpu_baseline` use; F_exec = 50*BH*pairs*D
+(25 contractions issued by the four-pass algorithm) is reported beside it.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+for _p in (ROOT, ROOT / "flash-hob_b200"):
+    if str(_p) not in sys.path:
+        sys.path.insert(0, str(_p))
+
+# name -> per-GPU shape.  "cfg5-shard" is 1/8 of the cross-attention scaling configuration
+# (B=16 H=32 -> 512 heads, 64 per GPU), so --gpus 8 is exactly that configuration.
+WORKLOADS = {
+    "cfg5-shard": dict(bh=64, n_q=4096, n_k=8192, d=128, causal=False, cot=1.0,
+                       desc="bf16 non-causal cross-attention N_Q=4096 N_K=8192 D=128, 64 heads per GPU "
+                            "(B=16 H=32 sharded 8 ways)"),
+    "cfg2": dict(bh=64, n_q=2048, n_k=2048, d=64, causal=False, cot=1.0,
+                 desc="bf16 non-causal B=4 H=16 N=2048 D=64"),
+    "cfg3": dict(bh=128, n_q=4096, n_k=4096, d=128, causal=True, cot=0.1,
+                 desc="bf16 causal B=8 H=16 N=4096 D=128, cotangents 0.1*N(0,1)"),
+    "cfg4-shard": dict(bh=4, n_q=32768, n_k=32768, d=128, causal=True, cot=1.0,
+                       desc="bf16 causal N=32768 D=128, 4 heads per GPU (B=1 H=32 sharded 8 ways)"),
+    "n8192": dict(bh=32, n_q=8192, n_k=8192, d=128, causal=False, cot=1.0,
+                  desc="bf16 non-causal B=1 H=32 N=8192 D=128"),
+}
+GEMM_UNITS = {"pass1": 3, "pass2": 5, "pass3": 9, "pass4": 8}
+# dram__bytes_read.sum + dram__bytes_write.sum of one pass-3 launch, from the ncu capture summarised
+# in profiles/ (captured on a smaller head count and scaled by heads); None until captured.
+PASS3_DRAM_BYTES_PER_HEAD = None
+
+
+def pairs(w):
+    if w["causal"]:
+        assert w["n_q"] == w["n_k"]
+        return w["n_q"] * (w["n_q"] + 1) // 2
+    return w["n_q"] * w["n_k"]
+
+
+def f_alg(w, heads=None):
+    return 24.0 * (w["bh"] if heads is None else heads) * pairs(w) * w["d"]
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return dict(burst=j["bf16_tflops"], sustained=j["bf16_tflops_sustained"], hbm=j["hbm_gbs"], src="measured")
+    return dict(burst=1590.0, sustained=1400.0, hbm=6650.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clk, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.strip().splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                clocks.append(float(f[0]))
+                max_clk = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not clocks:
+            return None
+        # the first samples can predate the load: take the median of the upper half
+        clocks.sort()
+        upper = clocks[len(clocks) // 2:]
+        return dict(sm_mhz=statistics.median(upper), sm_max_mhz=max_clk, reasons=sorted(reasons),
+                    samples=len(clocks))
+
+
+def make_batch(w, device, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    def rnd(n, s=1.0):
+        return (torch.randn(w["bh"], n, w["d"], generator=g, device=device, dtype=torch.float32) * s).bfloat16()
+    x = dict(q=rnd(w["n_q"]), k=rnd(w["n_k"]), v=rnd(w["n_k"]), do=rnd(w["n_q"], w["cot"]),
+             ddq=rnd(w["n_q"], w["cot"]), ddk=rnd(w["n_k"], w["cot"]), ddv=rnd(w["n_k"], w["cot"]))
+    return x
+
+
+def cpu_reference_sample(w, reps, warmup):
+    """The oracle's grad-of-grad (restatement of jax.vjp(attn_bwd)) on the host cores, one head per step."""
+    from oracle import attn_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(99)
+    x = [torch.randn(n, w["d"], generator=g).bfloat16().float()
+         for n in (w["n_q"], w["n_k"], w["n_k"], w["n_q"], w["n_q"], w["n_k"], w["n_k"])]
+    scale = w["d"] ** -0.5
+    times = []
+    for i in range(warmup + reps):
+        t0 = time.perf_counter()
+        O.bwdbwd_autograd(*x, scale, w["causal"])
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    sec = statistics.median(times)
+    return dict(value=f_alg(w, heads=1) / sec / 1e12, unit="TFLOP/s", cores=torch.get_num_threads(), kind="port",
+                sample=f"1 head of the workload per step (fp32 torch autograd-of-autograd of the first backward, "
+                       f"{reps} steps after {warmup} warm-up, median {sec*1e3:.0f} ms)"), sec
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    reps = max(1, args.steps)
+    cb, sec = cpu_reference_sample(w, reps, max(1, min(args.warmup, 2)))
+    line = dict(metric="double_backward_attention_tflops", value=cb["value"], unit="TFLOP/s", impl="reference",
+                n_gpus=args.gpus, steps=reps, warmup=max(1, min(args.warmup, 2)), ms_per_step=sec * 1e3,
+                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
+                config=dict(workload=args.workload, description=w["desc"], sample="1 head per step on host CPU"),
+                cpu_baseline=cb,
+                e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                note="reference XLA double-backward cannot run (jax is not installed); this is the CPU oracle "
+                     "port of jax.vjp(attn_bwd) on the box's host cores")
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="cfg5-shard", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    import fhob
+    from fhob import _lib
+    from fhob.ops import _Problem
+
+    warmup = max(3, args.warmup)
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    x = make_batch(w, dev, 1234 + rank)
+    scale = w["d"] ** -0.5
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=w["causal"])
+    args_dev = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
+    in_bytes = sum(t.numel() * t.element_size() for t in args_dev[:9])
+    out_bytes = 2 * (x["q"].numel() + x["k"].numel()) * 2
+
+    def step():
+        return fhob.flash_bwdbwd(*args_dev, is_causal=w["causal"])
+
+    # ---- device-resident timing
+    for _ in range(warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        outs = step()
+    e1.record()
+    barrier()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    clocks = sampler.stop() if sampler else None
+    ms_step = ms_total / args.steps
+    prob = _Problem(*args_dev, w["causal"], "auto")
+    status = prob.status()
+    if status != 0:
+        raise RuntimeError(f"device status {status} after the timed region")
+
+    # ---- per-pass timing (same stream, CUDA events between the stages)
+    lib = _lib.load()
+    stages = ["prepass", "pass1", "pass2", "pass3", "pass4"]
+    acc = {s: 0.0 for s in stages}
+    s_ptr = C.c_void_p(prob.stream)
+    for it in range(2 + args.steps):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
+        evs[0].record()
+        for i, s in enumerate(stages):
+            _lib.check(getattr(lib, f"fhob_{s}")(C.byref(prob.p), s_ptr), s)
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        if it >= 2:
+            for i, s in enumerate(stages):
+                acc[s] += evs[i].elapsed_time(evs[i + 1])
+    peaks = measured_peaks()
+    unit_flops = 2.0 * w["bh"] * pairs(w) * w["d"]
+    passes = {}
+    for s in stages:
+        ms = acc[s] / args.steps
+        passes[s] = dict(ms=round(ms, 4))
+        if s in GEMM_UNITS:
+            tf = GEMM_UNITS[s] * unit_flops / (ms * 1e-3) / 1e12
+            passes[s].update(tflops=round(tf, 1), frac_of_sustained_peak=round(tf / peaks["sustained"], 4))
+    dom = max(GEMM_UNITS, key=lambda s: passes[s]["ms"])
+    roofline = dict(bound="tensor", kernel=f"tc_pass_kernel<{dom[-1]}, {w['d']}, 64>", achieved=passes[dom]["tflops"],
+                    peak=peaks["sustained"], unit="TFLOP/s",
+                    frac=round(passes[dom]["tflops"] / peaks["sustained"], 4),
+                    frac_of_burst_peak=round(passes[dom]["tflops"] / peaks["burst"], 4),
+                    peak_source=f"{peaks['src']} cuBLAS bf16 (sustained, kernel timed inside a long step)",
+                    flops_basis=f"{GEMM_UNITS[dom]} contractions of 2*BH*pairs*D flop issued by this pass",
+                    traffic=(PASS3_DRAM_BYTES_PER_HEAD * w["bh"] if PASS3_DRAM_BYTES_PER_HEAD and dom == "pass3"
+                             else None))
+
+    # ---- end to end through the public entry point with host buffers
+    e2e = None
+    if not args.no_e2e:
+        host = [t.cpu().pin_memory() for t in args_dev[:9]]
+        for _ in range(2):
+            fhob.flash_bwdbwd(*host, scale, is_causal=w["causal"], device=dev)
+        barrier()
+        n_e2e = max(2, min(args.steps, 5))
+        e0.record()
+        for _ in range(n_e2e):
+            fhob.flash_bwdbwd(*host, scale, is_causal=w["causal"], device=dev)
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
+        e2e = dict(value=f_alg(w) * world / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms_e2e,
+                   h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes, steps=n_e2e)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_baseline, _ = cpu_reference_sample(w, reps=3, warmup=1)
+
+    value = f_alg(w) * world / (ms_step * 1e-3) / 1e12
+    line = dict(
+        metric="double_backward_attention_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps,
+        warmup=warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
+        data="synthetic",
+        config=dict(workload=args.workload, description=w["desc"], bh_per_gpu=w["bh"], n_q=w["n_q"], n_k=w["n_k"],
+                    d=w["d"], causal=w["causal"], parallelism=f"batch*heads sharded over {world} GPU(s), no collective",
+                    l2="inputs larger than L2: %.0f MB read per step" % (in_bytes / 1e6)),
+        per_gpu=dict(tflops_alg=value / world, tflops_exec=value / world * 50 / 24,
+                     frac_bf16_peak_alg=value / world / peaks["burst"],
+                     frac_bf16_peak_exec=value / world * 50 / 24 / peaks["burst"],
+                     frac_bf16_sustained_exec=value / world * 50 / 24 / peaks["sustained"]),
+        flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * 50 / 24),
+        passes=passes, roofline=roofline, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
+        gpu_launches=5 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
