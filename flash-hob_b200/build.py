@@ -14,7 +14,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "fhob" / "libfhob.so"
-SOURCES = ["fhob_api.cu", "simt_kernels.cu", "tc_kernels.cu"]
+SOURCES = ["fhob_api.cu", "simt_kernels.cu", "tc_kernels.cu", "static_scratch.cu"]
 HEADERS = ["fhob_common.cuh", "sm100_ptx.cuh", "../../include/fhob.h"]
 
 

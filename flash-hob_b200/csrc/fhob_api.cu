@@ -113,6 +113,8 @@ const char* fhob_strerror(int status) {
     case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes()";
     case FHOB_ERR_CUDA: return "a CUDA call failed (see fhob_last_cuda_error)";
     case FHOB_ERR_ARCH: return "the tensor-core kernels need a compute capability 10.x device";
+    case FHOB_ERR_STATIC_LIMIT: return "bh*n_q exceeds FHOB_STATIC_SCRATCH_MAX_ROWS, the capacity of the built-in "
+                                       "scratch array (use fhob_bwdbwd with a caller workspace)";
     default: break;
   }
   if (status & FHOB_ERR_TIMEOUT) return "device: a bounded wait ran out of iterations (results are invalid)";

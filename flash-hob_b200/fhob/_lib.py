@@ -14,8 +14,9 @@ ERR_TIMEOUT, ERR_SMEM_ALIGN = 64, 128
 SYMBOLS = (
     "fhob_version", "fhob_strerror", "fhob_last_cuda_error", "fhob_workspace_bytes", "fhob_bwdbwd",
     "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
-    "fhob_read_status", "fhob_forward",
+    "fhob_read_status", "fhob_forward", "fhob_bwdbwd_static_scratch",
 )
+STATIC_SCRATCH_MAX_ROWS = 262144
 
 
 class FhobProblem(C.Structure):
@@ -50,7 +51,7 @@ def load() -> C.CDLL:
     lib.fhob_workspace_bytes.restype = C.c_size_t
     lib.fhob_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
     for name in ("fhob_bwdbwd", "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass3", "fhob_pass4",
-                 "fhob_read_status"):
+                 "fhob_read_status", "fhob_bwdbwd_static_scratch"):
         fn = getattr(lib, name)
         fn.restype = C.c_int
         fn.argtypes = [P, C.c_void_p]

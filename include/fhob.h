@@ -45,6 +45,7 @@ enum {
   FHOB_ERR_WORKSPACE = 4,  /* workspace missing or too small */
   FHOB_ERR_CUDA = 5,       /* a CUDA runtime/driver call failed (see fhob_last_cuda_error) */
   FHOB_ERR_ARCH = 6,       /* tensor-core kernels need compute capability 10.x */
+  FHOB_ERR_STATIC_LIMIT = 7, /* fhob_bwdbwd_static_scratch: bh*n_q exceeds FHOB_STATIC_SCRATCH_MAX_ROWS */
   FHOB_ERR_TIMEOUT = 64,   /* device: a bounded mbarrier wait ran out (bit in the status word) */
   FHOB_ERR_SMEM_ALIGN = 128 /* device: dynamic shared memory base was not 1024-byte aligned */
 };
@@ -149,6 +150,40 @@ int fhob_read_status(const FhobProblem* p, void* stream);
  * writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).  CUDA-core kernel.
  */
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream);
+
+/*
+ * The operator for callers that cannot allocate device memory at all.
+ * (No counterpart in the reference, whose wrapper allocates its temporaries
+ * with torch on every call.)
+ *
+ * Who needs it: a host that owns all device memory itself and does not let an
+ * operator call cudaMalloc - an engine that carves everything out of one
+ * arena sized at start-up, a plug-in running inside another framework's
+ * memory plan, a latency-bound loop where an allocation could synchronise the
+ * device - and that has no spare buffer to lend as the workspace either.
+ * Same arguments and results as fhob_bwdbwd, except that p->workspace and
+ * p->workspace_bytes are ignored: the status word and the four row vectors
+ * live in a fixed device array inside the library (about 4 MiB, held on every
+ * GPU that loads the library until the process exits).  The call performs no
+ * cudaMalloc/cudaFree and calls no allocating library routine.
+ *
+ * Limit: bh * n_q <= FHOB_STATIC_SCRATCH_MAX_ROWS, otherwise
+ * FHOB_ERR_STATIC_LIMIT is returned and nothing is launched.
+ *
+ * The first call on each device looks up the device address of that array
+ * (one cudaGetSymbolAddress, with the calling thread's current device); make
+ * that first call before starting any stream capture on that device.
+ *
+ * All calls on a device share the one array, which still holds the previous
+ * call's row vectors; the operator clears the status word itself and writes
+ * every entry before reading it, so nothing has to be reset between calls.
+ * Because of the sharing, two calls whose kernels can overlap on the GPU (two
+ * streams, two host threads on one device) race on the array: issue these
+ * calls on one stream, or otherwise order them.  fhob_read_status() does not
+ * see this array; a timed-out wait shows up as wrong results only.
+ */
+#define FHOB_STATIC_SCRATCH_MAX_ROWS 262144
+int fhob_bwdbwd_static_scratch(const FhobProblem* p, void* stream);
 
 #ifdef __cplusplus
 }
