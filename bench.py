@@ -83,7 +83,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             pass
 
@@ -168,14 +168,18 @@ def run_reference(args, w, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg5-shard", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--heads", type=int, default=0, help="heads per GPU (default: the workload's); "
+                    "smaller values give the small cases profiler captures need")
     args = ap.parse_args()
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.heads > 0:
+        w["bh"] = args.heads
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -200,14 +204,15 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    from fhob.sharding import head_shard, max_over_ranks as _max_over_ranks
 
-    x = make_batch(w, dev, 1234 + rank)
+    def max_over_ranks(ms):
+        return _max_over_ranks(ms, device=dev)
+
+    # weak scaling: the job has bh*world heads and every rank owns a contiguous shard of bh of them
+    shard_start, shard_heads = head_shard(w["bh"] * world, world, rank)
+    assert shard_heads == w["bh"]
+    x = make_batch(w, dev, 1234 + shard_start)
     scale = w["d"] ** -0.5
     o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=w["causal"])
     args_dev = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
