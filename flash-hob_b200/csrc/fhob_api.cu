@@ -21,11 +21,11 @@ void set_cuda_error_text(const char* text) { std::snprintf(g_cuda_error, sizeof(
 
 namespace {
 
-// One warp per query row: D = sum_d dO*O, then the two folded vectors.
+// One warp per query row: D = sum_d dO*O, stored as k1 = -D, and nlc = -L*log2(e).
 // Block 0 also clears the status word, so every operator call starts clean.
 template <typename T>
 __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                               float* __restrict__ nlc, float* __restrict__ nds, int* status, long rows, int d,
+                               float* __restrict__ nlc, float* __restrict__ k1, int* status, long rows, int d,
                                float scale) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
   long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -38,18 +38,18 @@ __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
-    nds[row] = -acc * scale;
+    k1[row] = -acc;
     nlc[row] = -lse[row] * kLog2e;
   }
 }
 
-__global__ void row_stats_kernel(const float* nds, const float* ndd, const float* nbs, float* d_out, float* dd_out,
-                                 float* b_out, long rows, float inv_scale) {
+__global__ void row_stats_kernel(const float* k1, const float* ndd, const float* k23, float* d_out, float* dd_out,
+                                 float* b_out, long rows) {
   long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= rows) return;
-  if (d_out) d_out[i] = -nds[i] * inv_scale;
+  if (d_out) d_out[i] = -k1[i];
   if (dd_out) dd_out[i] = -ndd[i];
-  if (b_out) b_out[i] = -nbs[i] * inv_scale;
+  if (b_out) b_out[i] = -(k23[i] + k1[i] * ndd[i]);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -141,11 +141,11 @@ int fhob_prepass(const FhobProblem* p, void* stream) {
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
   if (p->dtype == FHOB_BF16) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.nds,
+        static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
         rv.status, rows, p->d, p->scale);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
-                                                      static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.nds,
+                                                      static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
                                                       rv.status, rows, p->d, p->scale);
   }
   FHOB_CUDA_OK(cudaGetLastError());
@@ -177,8 +177,8 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
   RowVectors rv = row_vectors(*p);
   long rows = static_cast<long>(p->bh) * p->n_q;
   unsigned grid = static_cast<unsigned>((rows + 255) / 256);
-  row_stats_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(rv.nds, rv.ndd, rv.nbs, d_out, dd_out, b_out,
-                                                                        rows, 1.f / p->scale);
+  row_stats_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(rv.k1, rv.ndd, rv.k23, d_out, dd_out, b_out,
+                                                                        rows);
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
 }

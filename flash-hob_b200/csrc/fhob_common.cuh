@@ -10,9 +10,11 @@
 //   dQ2 = dS ddK + dS2 K           ddO = ddP V + P ddV
 //   dK2 = dS^T ddQ + dS2^T Q       dV2 = ddP^T dO
 //
-// The four row vectors are staged in the workspace with sign and scale folded
-// in, so the per-element work is FMAs only:
-//   nlc = -L*log2(e)   nds = -D*scale   ndd = -dd   nbs = -b*scale
+// Four row vectors are staged in the workspace with signs folded in so that the
+// per-element work is a few FMAs (dP' = dP + k1, X' = X + k23, t = scale*A2 + ndd):
+//   nlc = -L*log2(e)   k1 = -D   ndd = -dd   k23 = -D*dd - b
+//   P = exp2(S_raw*scale*log2e + nlc)       ddP = P t
+//   dS = (P scale) dP'                      dS2 = (P scale) (dP' t + X')
 #pragma once
 
 #include <cuda_bf16.h>
@@ -30,9 +32,9 @@ constexpr int kWorkspaceTailBytes = 1024;
 struct RowVectors {
   int* status;  // device status word (workspace header)
   float* nlc;   // -L * log2(e)
-  float* nds;   // -D * scale
+  float* k1;    // -D
   float* ndd;   // -dd
-  float* nbs;   // -b * scale
+  float* k23;   // -D*dd - b
 };
 
 inline RowVectors row_vectors(const FhobProblem& p) {
@@ -42,9 +44,9 @@ inline RowVectors row_vectors(const FhobProblem& p) {
   r.status = reinterpret_cast<int*>(base);
   float* f = reinterpret_cast<float*>(base + kWorkspaceHeaderBytes);
   r.nlc = f;
-  r.nds = f + n;
+  r.k1 = f + n;
   r.ndd = f + 2 * n;
-  r.nbs = f + 3 * n;
+  r.k23 = f + 3 * n;
   return r;
 }
 

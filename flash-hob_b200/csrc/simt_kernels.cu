@@ -25,8 +25,8 @@ constexpr int DCH = 4;        // output columns per thread and row: lane + 32*m,
 struct SimtParams {
   const void *q, *k, *v, *d_o, *ddq, *ddk, *ddv;
   void *dq2, *dk2, *dv2, *ddo;
-  const float *nlc, *nds;
-  float *ndd, *nbs;
+  const float *nlc, *k1;
+  float *ndd, *k23;
   int n_q, n_k, d, causal;
   float scale;
 };
@@ -113,15 +113,17 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   }
 
   // per-row constants of the stationary queries (passes 1-3)
-  float r_nlc[RPW], r_nds[RPW], r_ndd[RPW], r_nbs[RPW], rowacc[RPW];
+  float r_nlc[RPW], r_k1[RPW], r_nds[RPW], r_ndd[RPW], r_nbs[RPW], rowacc[RPW];
 #pragma unroll
   for (int i = 0; i < RPW; ++i) {
     int qi = m0 + warp * RPW + i;
     bool ok = kQStationary && qi < p.n_q;
     r_nlc[i] = ok ? p.nlc[voff + qi] : 0.f;
-    r_nds[i] = ok && PASS >= 2 ? p.nds[voff + qi] : 0.f;
+    const float k1 = ok && PASS >= 2 ? p.k1[voff + qi] : 0.f;
+    r_k1[i] = k1;
+    r_nds[i] = k1 * p.scale;                                                    // -D*scale
     r_ndd[i] = ok && PASS >= 2 ? p.ndd[voff + qi] : 0.f;
-    r_nbs[i] = ok && PASS >= 3 ? p.nbs[voff + qi] : 0.f;
+    r_nbs[i] = ok && PASS >= 3 ? (p.k23[voff + qi] + k1 * r_ndd[i]) * p.scale : 0.f;  // -b*scale
     rowacc[i] = 0.f;
   }
   float out0[RPW][DCH], out1[RPW][DCH];
@@ -162,9 +164,10 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
         int qi = n0 + threadIdx.x;
         bool ok = qi < p.n_q;
         svec[0 * TN + threadIdx.x] = ok ? p.nlc[voff + qi] : 0.f;
-        svec[1 * TN + threadIdx.x] = ok ? p.nds[voff + qi] : 0.f;
-        svec[2 * TN + threadIdx.x] = ok ? p.ndd[voff + qi] : 0.f;
-        svec[3 * TN + threadIdx.x] = ok ? p.nbs[voff + qi] : 0.f;
+        const float k1 = ok ? p.k1[voff + qi] : 0.f, ndd = ok ? p.ndd[voff + qi] : 0.f;
+        svec[1 * TN + threadIdx.x] = k1 * p.scale;
+        svec[2 * TN + threadIdx.x] = ndd;
+        svec[3 * TN + threadIdx.x] = ok ? (p.k23[voff + qi] + k1 * ndd) * p.scale : 0.f;
       }
     }
     __syncthreads();
@@ -265,7 +268,7 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
       int qi = m0 + warp * RPW + i;
       if (lane == 0 && qi < p.n_q) {
         if (PASS == 1) p.ndd[voff + qi] = -p.scale * tot;          // -dd, dd = scale * sum P A2
-        else p.nbs[voff + qi] = -p.scale * tot;                    // -b*scale
+        else p.k23[voff + qi] = -r_k1[i] * r_ndd[i] - tot;          // -D*dd - b, b = sum P dP2
       }
     }
   } else {
@@ -389,7 +392,7 @@ SimtParams make_params(const FhobProblem& p) {
   SimtParams s;
   s.q = p.q; s.k = p.k; s.v = p.v; s.d_o = p.d_o; s.ddq = p.ddq; s.ddk = p.ddk; s.ddv = p.ddv;
   s.dq2 = p.dq2; s.dk2 = p.dk2; s.dv2 = p.dv2; s.ddo = p.ddo;
-  s.nlc = rv.nlc; s.nds = rv.nds; s.ndd = rv.ndd; s.nbs = rv.nbs;
+  s.nlc = rv.nlc; s.k1 = rv.k1; s.ndd = rv.ndd; s.k23 = rv.k23;
   s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.causal = p.causal; s.scale = p.scale;
   return s;
 }

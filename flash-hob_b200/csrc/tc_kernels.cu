@@ -10,19 +10,25 @@
 // TMEM lanes, and streams BN-row tiles of the other side:
 //
 //   score-shaped accumulators (128 x BN fp32 each, K-major smem x K-major smem):
-//     S  = stat0 . strm0^T          A2 = stat1 . strm0^T + stat0 . strm1^T
-//     dP = stat2 . strm2^T          X  = stat2 . strm3^T            (pass 4: X = stat3 . strm2^T)
+//     group A:  [S | stat0.strm1^T] = stat0 . [strm0 ; strm1]^T     A2 += stat1 . strm0^T
+//     group B:  [dP | X] = stat2 . [strm2 ; strm3]^T      (pass 4: dP = stat2.strm2^T, X = stat3.strm2^T)
 //   output accumulators (128 x D fp32 each, A = bf16 tile in TMEM, B = streamed tile read MN-major):
-//     pass 3: dQ2 += dS . ddK + dS2 . K       ddO += ddP . V + P . ddV
-//     pass 4: dK2 += dS^T . ddQ + dS2^T . Q   dV2 += ddP^T . dO
+//     pass 3: ddO += ddP . V + P . ddV   (after group A)     dQ2 += dS . ddK + dS2 . K     (after group B)
+//     pass 4: dV2 += ddP^T . dO          (after group A)     dK2 += dS^T . ddQ + dS2^T . Q (after group B)
 //
-// Warp roles (320 threads): warps 0-7 elementwise (warp w owns TMEM lanes
-// 32*(w%4).., column half w/4), warp 8 = TMA producer (one lane), warp 9 =
-// MMA issuer (one lane) and TMEM allocator.  Every mbarrier wait is bounded:
-// when it runs out the CTA raises the status word, drains and exits.
+// Warp roles (320 threads): warp 0 = MMA issuer (one lane) and TMEM allocator, warp 1 = TMA
+// producer (one lane), warps 2-9 elementwise (warp w owns TMEM lanes 32*(w%4).., column half
+// (w-2)/4).
+//   passes 1, 2: two score stages in TMEM; the MMA warp runs one tile ahead.
+//   passes 3, 4: TMEM is full with one stage (2*D + 4*64 columns), so the tile is pipelined in
+//   two halves instead: while the elementwise warps turn group A into P / ddP, the tensor core
+//   computes group B; while they turn group B into dS / dS2, it runs the group-A outputs and
+//   group A of the next tile.  The bf16 tiles overwrite their own accumulators in place.
+// Every mbarrier wait is bounded: when it runs out the CTA raises the status word, drains and exits.
 #include <cuda.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "fhob_common.cuh"
@@ -35,8 +41,9 @@ using namespace ptx;
 
 constexpr int BM = 128;
 constexpr int EW_THREADS = 256;
-constexpr int TMA_WARP = 8;
-constexpr int MMA_WARP = 9;
+constexpr int MMA_WARP = 0;  // lowest warp id: the schedulers favour it over the elementwise warps
+constexpr int TMA_WARP = 1;
+constexpr int EW_WARP0 = 2;  // elementwise warps 2..9
 constexpr int NTHREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KB per CTA
@@ -52,41 +59,69 @@ struct Cfg {
   static constexpr int NOUT = PASS >= 3 ? 2 : 0;
   static constexpr int OUT_COLS = NOUT * D;
   static constexpr int STAGE_COLS = NACC * BN;
-  static constexpr int NSS = (TMEM_COLS - OUT_COLS) / STAGE_COLS >= 2 ? 2 : 1;  // score stages in TMEM
+  // score stages in TMEM: two for the reducing passes, one (pipelined in halves) for passes 3, 4
+  static constexpr int NSS = PASS <= 2 ? ((TMEM_COLS - OUT_COLS) / STAGE_COLS >= 2 ? 2 : 1) : 1;
   static constexpr int STAT_BYTES = BM * D * 2;
   static constexpr int STRM_BYTES = BN * D * 2;
-  static constexpr int SLOT_BYTES = NSTRM * STRM_BYTES;
+  // pass 4: the four per-query constant vectors of the streamed queries travel with the slot
+  static constexpr int STATS_BYTES = PASS == 4 ? 4 * BN * 4 : 0;
+  static constexpr int SLOT_BYTES = NSTRM * STRM_BYTES + STATS_BYTES;
   static constexpr int NSLOT_FIT = (SMEM_LIMIT - SMEM_TAIL - NSTAT * STAT_BYTES) / SLOT_BYTES;
   static constexpr int NSLOT = NSLOT_FIT > 4 ? 4 : NSLOT_FIT;
   static constexpr int SMEM_BYTES = NSTAT * STAT_BYTES + NSLOT * SLOT_BYTES + SMEM_TAIL;
-  static constexpr int CH = BN / 32;  // 16-column chunks per elementwise thread (it owns BN/2 columns)
+  // Streamed tiles 2p and 2p+1 form a pair whose 64-column boxes interleave in shared memory
+  // (box b of tile 2p, box b of tile 2p+1, box b+1 of tile 2p, ...), so that one K-major operand
+  // descriptor can cover both tiles stacked as 2*BN rows: products that share their A operand
+  // (S and Q.ddK^T; dP and X) are then issued as one MMA with N = 2*BN.  Shared-memory operand
+  // bandwidth bounds an SS MMA at about 128 B/clk; N = 64 moves 6 KB per 32 tensor cycles and runs
+  // at half rate, N >= 128 runs at full rate.  An unpaired last tile keeps the compact layout.
+  __host__ __device__ static constexpr bool paired(int i) { return (i / 2) * 2 + 1 < NSTRM; }
+  __host__ __device__ static constexpr int strm_base(int i) {
+    return (i / 2) * 2 * STRM_BYTES + (paired(i) ? (i % 2) * BN * 128 : 0);
+  }
+  __host__ __device__ static constexpr int strm_box(int i) { return paired(i) ? 2 * BN * 128 : BN * 128; }
   static_assert(NSS * STAGE_COLS + OUT_COLS <= TMEM_COLS, "TMEM budget");
   static_assert(NSLOT >= 2, "need two streamed slots");
   static_assert(D == 64 || D == 128, "head dim");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "streamed tile");
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 128, "streamed tile");
+  static_assert(PASS <= 2 || BN == 64, "passes 3 and 4 are written for 64-row streamed tiles");
 };
 
 struct TcParams {
   CUtensorMap stat[4];
   CUtensorMap strm[4];
-  const float* nlc;
-  const float* nds;
-  float* ndd;
-  float* nbs;
+  const float* nlc;  // -L*log2(e)
+  const float* k1;   // -D
+  float* ndd;        // -dd           (written by pass 1)
+  float* k23;        // -D*dd - b     (written by pass 2)
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int* status;
   int n_q, n_k, causal, tiles_per_head;
   float scale;
+#ifdef FHOB_TC_PROFILE
+  unsigned long long* prof;
+#endif
 };
+
+// Optional cycle accounting of the three roles (compile with -DFHOB_TC_PROFILE; development aid).
+#ifdef FHOB_TC_PROFILE
+#define PROF_DECL long long prof_t[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t0 = clock64();
+#define PROF_MARK(i) { long long now__ = clock64(); prof_t[i] += now__ - prof_t0; prof_t0 = now__; }
+#define PROF_FLUSH(base) for (int i__ = 0; i__ < 8; ++i__) atomicAdd(&p.prof[(base) + i__], (unsigned long long)prof_t[i__]);
+#else
+#define PROF_DECL
+#define PROF_MARK(i)
+#define PROF_FLUSH(base)
+#endif
 
 struct Bars {
   uint64_t stat_full;
   uint64_t strm_full[4];
   uint64_t strm_free[4];
-  uint64_t s_full[2];
-  uint64_t s_free[2];
-  uint64_t p_full;
+  uint64_t s_full[2];   // passes 1, 2: per score stage; passes 3, 4: [0] = group A done, [1] = group B done
+  uint64_t s_free[2];   // passes 1, 2: stage consumed by the elementwise warps
+  uint64_t p_full[2];   // passes 3, 4: [0] = P/ddP written, [1] = dS/dS2 written
   uint64_t out_full;
   uint64_t teardown;
   uint32_t tmem_base;
@@ -114,30 +149,179 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, Bars* b
   }
 }
 
-// D (+)= A . B^T with both tiles K-major in shared memory (rows of 64-element boxes, 128B swizzle).
-template <int D, int A_ROWS, int B_ROWS>
-__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint32_t a_tile, uint32_t b_tile, uint32_t idesc,
+// Descriptor words of 128-byte-swizzled bf16 tiles (rows of 64 elements, 8-row groups 1024 B apart).
+constexpr uint32_t kDescHi = umma_desc_hi_sw128(1024);
+
+// D (+)= A . B^T with both tiles K-major in shared memory.  a_lo / b_lo are the low descriptor
+// words of the tiles; a K=16 step advances 32 bytes inside a 64-column box, the second box of a
+// D=128 tile starts A_BOX / B_BOX bytes after the first.  The number of B rows (N) is in idesc.
+template <int D, int A_BOX, int B_BOX>
+__device__ __forceinline__ void gemm_ss(bool leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
                                         bool accumulate) {
 #pragma unroll
   for (int ks = 0; ks < D / 16; ++ks) {
-    uint32_t a = a_tile + (ks / 4) * (A_ROWS * 128) + (ks % 4) * 32;
-    uint32_t b = b_tile + (ks / 4) * (B_ROWS * 128) + (ks % 4) * 32;
-    umma_ss(d_tmem, umma_desc_sw128(a, 16, 1024), umma_desc_sw128(b, 16, 1024), idesc, (accumulate || ks > 0) ? 1u : 0u);
+    const uint32_t a = a_lo + (((ks / 4) * A_BOX + (ks % 4) * 32) >> 4);
+    const uint32_t b = b_lo + (((ks / 4) * B_BOX + (ks % 4) * 32) >> 4);
+    if (leader) umma_ss_split(d_tmem, a, b, kDescHi, idesc, (accumulate || ks > 0) ? 1u : 0u);
   }
 }
 
-// D (+)= A . B with A = bf16 tile in TMEM (128 x BN, 8 columns per 16 keys) and B = streamed
-// tile (BN rows x D) read MN-major: the contraction runs down the BN rows.
+// D (+)= A . B with A = bf16 tile in TMEM (128 x BN, 8 columns per 16 rows of B) and B = streamed
+// tile (BN rows x D) read MN-major: the contraction runs down the BN rows, 2048 bytes per step.
+// b_lo must carry the leading byte offset (distance between the two 64-column boxes).
 template <int D, int BN>
-__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_region, uint32_t b_tile, uint32_t idesc,
-                                        bool accumulate) {
+__device__ __forceinline__ void gemm_ts(bool leader, uint32_t d_tmem, uint32_t a_region, uint32_t b_lo,
+                                        uint32_t idesc, bool accumulate) {
   constexpr int CH = BN / 32;
 #pragma unroll
   for (int s = 0; s < BN / 16; ++s) {
-    uint32_t a = a_region + (s / CH) * (BN / 2) + 8 * (s % CH);
-    uint32_t b = b_tile + s * 2048;
-    umma_ts(d_tmem, a, umma_desc_sw128(b, BN * 128, 1024), idesc, (accumulate || s > 0) ? 1u : 0u);
+    const uint32_t a = a_region + (s / CH) * (BN / 2) + 8 * (s % CH);
+    if (leader) umma_ts_split(d_tmem, a, b_lo + ((s * 2048) >> 4), kDescHi, idesc, (accumulate || s > 0) ? 1u : 0u);
   }
+}
+
+struct EwCtx {
+  float scale, sl2;
+  float r_nlc, r_k1, r_ndd, r_k23;  // constants of this thread's query row (passes 1-3)
+  uint32_t sv;                      // pass 4: shared-memory address of the slot's [nlc|ndd|k1|k23][64] block
+  int lo, hi;                       // visible streamed index range of this thread's row
+};
+
+__device__ __forceinline__ void load4(uint32_t smem_addr, float (&v)[4]) {
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(smem_addr));
+}
+
+// Passes 1 and 2: row reductions over one streamed tile.  acc = TMEM address of the stage (lane
+// and column-half offset included); col_base = streamed index of the thread's first column.
+template <int PASS, int BN, bool MASKED>
+__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float& rowacc) {
+  constexpr int CH = BN / 32;
+  const float nds = c.r_k1 * c.scale;  // -D*scale
+#pragma unroll
+  for (int ch = 0; ch < CH; ++ch) {
+    const int col0 = col_base + 16 * ch;
+    uint32_t s[16], a2[16], dp[16], x[16];
+    tmem_ld16(acc + 0 * BN + 16 * ch, s);
+    tmem_ld16(acc + 1 * BN + 16 * ch, a2);
+    if (PASS == 2) {
+      tmem_ld16(acc + 2 * BN + 16 * ch, dp);
+      tmem_ld16(acc + 3 * BN + 16 * ch, x);
+    }
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float fs = __uint_as_float(s[j]), fa2 = __uint_as_float(a2[j]);
+      float pr = ex2(fmaf(fs, c.sl2, c.r_nlc));
+      if (MASKED) {
+        const int idx = col0 + j;
+        pr = (idx >= c.lo && idx <= c.hi) ? pr : 0.f;
+      }
+      if (PASS == 1) {
+        rowacc = fmaf(pr, fa2, rowacc);
+      } else {
+        const float tt = fmaf(fa2, c.scale, c.r_ndd);
+        float u = fmaf(__uint_as_float(dp[j]), tt, __uint_as_float(x[j]));
+        u = fmaf(nds, fa2, u);
+        rowacc = fmaf(pr, u, rowacc);
+      }
+    }
+  }
+}
+
+// Passes 3 and 4 work on a thread's 32 columns of a 64-row streamed tile at once, two columns
+// per packed fp32 instruction (fma/mul/add .f32x2).
+__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) {
+  return make_float2(__uint_as_float(lo), __uint_as_float(hi));
+}
+
+// First half of a tile: S, A2 -> P = exp2(S*sl2 + nlc), t = scale*A2 - dd; writes ddP = P t (and P
+// in pass 3) as bf16 over the accumulators and keeps P*scale and t in registers for the second half.
+template <int PASS, bool MASKED>
+__device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
+                                          float2 (&ps)[16], float2 (&tt)[16]) {
+  constexpr bool kQStat = PASS != 4;
+  constexpr int BN = 64;
+  uint32_t s[32], a2[32];
+  tmem_ld32(acc + 0 * BN, s);
+  tmem_ld32(acc + 1 * BN, a2);
+  tmem_wait_ld();
+  uint32_t w_ddp[16], w_p[16];
+  const float2 sl2 = make_float2(c.sl2, c.sl2), scale = make_float2(c.scale, c.scale);
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    float c_nlc[4], c_ndd[4];
+    if (kQStat) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { c_nlc[e] = c.r_nlc; c_ndd[e] = c.r_ndd; }
+    } else {
+      load4(c.sv + (0 * BN + col_in_tile + 4 * j4) * 4, c_nlc);
+      load4(c.sv + (1 * BN + col_in_tile + 4 * j4) * 4, c_ndd);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = 4 * j4 + 2 * h;  // columns j, j+1
+      const float2 arg = __ffma2_rn(f2(s[j], s[j + 1]), sl2, make_float2(c_nlc[2 * h], c_nlc[2 * h + 1]));
+      float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+      float2 t = __ffma2_rn(f2(a2[j], a2[j + 1]), scale, make_float2(c_ndd[2 * h], c_ndd[2 * h + 1]));
+      if (MASKED) {
+        const int idx = col_base + j;
+        const bool ok0 = idx >= c.lo && idx <= c.hi, ok1 = idx + 1 >= c.lo && idx + 1 <= c.hi;
+        pr.x = ok0 ? pr.x : 0.f; pr.y = ok1 ? pr.y : 0.f;
+        t.x = ok0 ? t.x : 0.f;   t.y = ok1 ? t.y : 0.f;
+      }
+      const float2 ddp = __fmul2_rn(pr, t);
+      ps[j / 2] = __fmul2_rn(pr, scale);
+      tt[j / 2] = t;
+      w_ddp[j / 2] = pack_bf16(ddp.x, ddp.y);
+      if (PASS == 3) w_p[j / 2] = pack_bf16(pr.x, pr.y);
+    }
+  }
+  // the bf16 tiles overwrite accumulator columns this thread has already consumed
+  tmem_st16(acc + 1 * BN, w_ddp);
+  if (PASS == 3) tmem_st16(acc + 0 * BN, w_p);
+}
+
+// Second half: dP' = dP - D, X' = X - D*dd - b, dS = (P scale) dP', dS2 = (P scale)(dP' t + X').
+template <int PASS, bool MASKED>
+__device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
+                                          const float2 (&ps)[16], const float2 (&tt)[16]) {
+  constexpr bool kQStat = PASS != 4;
+  constexpr int BN = 64;
+  uint32_t dp[32], x[32];
+  tmem_ld32(acc + 2 * BN, dp);
+  tmem_ld32(acc + 3 * BN, x);
+  tmem_wait_ld();
+  uint32_t w_ds[16], w_ds2[16];
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    float c_k1[4], c_k23[4];
+    if (kQStat) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { c_k1[e] = c.r_k1; c_k23[e] = c.r_k23; }
+    } else {
+      load4(c.sv + (2 * BN + col_in_tile + 4 * j4) * 4, c_k1);
+      load4(c.sv + (3 * BN + col_in_tile + 4 * j4) * 4, c_k23);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int j = 4 * j4 + 2 * h;
+      const float2 dpp = __fadd2_rn(f2(dp[j], dp[j + 1]), make_float2(c_k1[2 * h], c_k1[2 * h + 1]));
+      const float2 xp = __fadd2_rn(f2(x[j], x[j + 1]), make_float2(c_k23[2 * h], c_k23[2 * h + 1]));
+      const float2 u = __ffma2_rn(dpp, tt[j / 2], xp);
+      float2 ds = __fmul2_rn(ps[j / 2], dpp);
+      float2 ds2 = __fmul2_rn(ps[j / 2], u);
+      if (MASKED) {
+        const int idx = col_base + j;
+        const bool ok0 = idx >= c.lo && idx <= c.hi, ok1 = idx + 1 >= c.lo && idx + 1 <= c.hi;
+        ds.x = ok0 ? ds.x : 0.f;   ds.y = ok1 ? ds.y : 0.f;
+        ds2.x = ok0 ? ds2.x : 0.f; ds2.y = ok1 ? ds2.y : 0.f;
+      }
+      w_ds[j / 2] = pack_bf16(ds.x, ds.y);
+      w_ds2[j / 2] = pack_bf16(ds2.x, ds2.y);
+    }
+  }
+  tmem_st16(acc + 2 * BN, w_ds);
+  tmem_st16(acc + 3 * BN, w_ds2);
 }
 
 template <int PASS, int D, int BN>
@@ -184,8 +368,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->s_free[i], EW_THREADS);
+      mbar_init(&bars->p_full[i], EW_THREADS);
     }
-    mbar_init(&bars->p_full, EW_THREADS);
     mbar_init(&bars->out_full, 1);
     mbar_init(&bars->teardown, 1);
     bars->abort_flag = 0;
@@ -213,18 +397,31 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           tma_load_3d(stat_tiles + i * C::STAT_BYTES + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
                       head);
       int issued = 0;
+      PROF_DECL
       for (int it = 0; it < n_iter; ++it) {
         const int slot = it % C::NSLOT;
+        PROF_MARK(7)
         if (!wait_bar(&bars->strm_free[slot], ((it / C::NSLOT) & 1) ^ 1, bars, p.status)) break;
+        PROF_MARK(0)
         mbar_arrive_expect_tx(&bars->strm_full[slot], C::SLOT_BYTES);
         uint8_t* dst = strm_tiles + slot * C::SLOT_BYTES;
         const int n0 = (t_begin + it) * BN;
         for (int i = 0; i < C::NSTRM; ++i)
           for (int bx = 0; bx < D / 64; ++bx)
-            tma_load_3d(dst + i * C::STRM_BYTES + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
-                        head);
+            tma_load_3d(dst + C::strm_base(i) + bx * C::strm_box(i), &p.strm[i], &bars->strm_full[slot], bx * 64,
+                        n0, head);
+        if (PASS == 4) {
+          const size_t vo = static_cast<size_t>(head) * p.n_q + n0;
+          uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
+          bulk_load(sv + 0 * BN * 4, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
+          bulk_load(sv + 1 * BN * 4, p.ndd + vo, BN * 4, &bars->strm_full[slot]);
+          bulk_load(sv + 2 * BN * 4, p.k1 + vo, BN * 4, &bars->strm_full[slot]);
+          bulk_load(sv + 3 * BN * 4, p.k23 + vo, BN * 4, &bars->strm_full[slot]);
+        }
         issued = it + 1;
+        PROF_MARK(1)
       }
+      PROF_FLUSH(16)
       // drain: every load issued above must have landed before the CTA may exit
       wait_bar(&bars->stat_full, 0, bars, p.status);
       for (int it = issued > C::NSLOT ? issued - C::NSLOT : 0; it < issued; ++it) {
@@ -240,60 +437,120 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     }
   } else if (warp == MMA_WARP) {
     // ================================================= MMA issuer
-    if (lane == 0 && n_iter > 0) {
-      constexpr uint32_t idesc_s = umma_idesc_bf16(BM, BN, false, false);
+    // The whole warp runs the loop so that addresses and descriptors stay warp-uniform; one lane
+    // issues the MMAs and commits.
+    if (n_iter > 0) {
+      const bool leader = lane == 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, wait_bar(bar, parity, bars, p.status)) != 0;
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) umma_commit(bar);
+      };
+      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false);      // one streamed tile
+      constexpr uint32_t idesc_s2 = umma_idesc_bf16(BM, 2 * BN, false, false);  // a stacked pair
       constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true);
-      const uint32_t stat_base = smem_u32(stat_tiles);
-      bool ok = wait_bar(&bars->stat_full, 0, bars, p.status);
-      for (int it = 0; ok && it < n_iter; ++it) {
+      constexpr int kStatBox = BM * 128;
+      // low descriptor words of the tiles: K-major use (LBO field unused, set to 1) and MN-major
+      // use of streamed tile i (LBO = distance between its two 64-column boxes)
+      const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
+      const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
+      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4;
+      auto k_lo = [&](uint32_t slot_lo, int i) { return slot_lo + (C::strm_base(i) >> 4); };
+      auto mn_lo = [&](uint32_t slot_lo, int i) {
+        return slot_lo - (1u << 16) + (C::strm_base(i) >> 4) + (static_cast<uint32_t>(C::strm_box(i) >> 4) << 16);
+      };
+      bool ok = wait_all(&bars->stat_full, 0);
+      PROF_DECL
+
+      // group A of tile `it`: [S | stat0.strm1^T] as one N = 2*BN product, then A2 += stat1.strm0^T
+      auto issue_group_a = [&](int it, uint32_t acc) -> bool {
         const int slot = it % C::NSLOT;
-        const int stage = it % C::NSS;
-        ok = wait_bar(&bars->strm_full[slot], (it / C::NSLOT) & 1, bars, p.status);
-        if (!ok) break;
-        if (PASS <= 2) {
-          ok = wait_bar(&bars->s_free[stage], ((it / C::NSS) & 1) ^ 1, bars, p.status);
-          if (!ok) break;
-        }
+        PROF_MARK(7)
+        if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
+        PROF_MARK(0)
         tc_fence_after();
-        const uint32_t strm_base = smem_u32(strm_tiles + slot * C::SLOT_BYTES);
-        const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
-        auto st = [&](int i) { return stat_base + i * C::STAT_BYTES; };
-        auto sr = [&](int i) { return strm_base + i * C::STRM_BYTES; };
-        // score-shaped accumulators
-        gemm_ss<D, BM, BN>(acc + 0 * BN, st(0), sr(0), idesc_s, false);  // S
-        if (kQStat) {
-          gemm_ss<D, BM, BN>(acc + 1 * BN, st(1), sr(0), idesc_s, false);  // ddQ K^T
-          gemm_ss<D, BM, BN>(acc + 1 * BN, st(0), sr(1), idesc_s, true);   // + Q ddK^T
+        const uint32_t sl = strm_lo + slot * kSlot16;
+        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
+        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
+        return true;
+      };
+      // group B of tile `it`: [dP | X] (one stacked product in passes 2, 3; two products in pass 4)
+      auto issue_group_b = [&](int it, uint32_t acc) {
+        const uint32_t sl = strm_lo + (it % C::NSLOT) * kSlot16;
+        if (PASS == 4) {
+          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s1, false);
+          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_lo + 3 * kStat16, k_lo(sl, 2), idesc_s1, false);
         } else {
-          gemm_ss<D, BM, BN>(acc + 1 * BN, st(0), sr(1), idesc_s, false);  // K ddQ^T
-          gemm_ss<D, BM, BN>(acc + 1 * BN, st(1), sr(0), idesc_s, true);   // + ddK Q^T
+          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s2, false);
         }
-        if (PASS >= 2) {
-          gemm_ss<D, BM, BN>(acc + 2 * BN, st(2), sr(2), idesc_s, false);  // dP
-          if (kQStat) gemm_ss<D, BM, BN>(acc + 3 * BN, st(2), sr(3), idesc_s, false);  // dO ddV^T
-          else gemm_ss<D, BM, BN>(acc + 3 * BN, st(3), sr(2), idesc_s, false);         // ddV dO^T
-        }
-        umma_commit(&bars->s_full[stage]);
-        if (PASS <= 2) {
-          umma_commit(&bars->strm_free[slot]);
-        } else {
-          ok = wait_bar(&bars->p_full, it & 1, bars, p.status);
+      };
+
+      if (PASS <= 2) {
+        for (int it = 0; ok && it < n_iter; ++it) {
+          const int stage = it % C::NSS;
+          const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+          PROF_MARK(7)
+          ok = wait_all(&bars->s_free[stage], ((it / C::NSS) & 1) ^ 1);
+          PROF_MARK(1)
+          ok = ok && issue_group_a(it, acc);
           if (!ok) break;
-          tc_fence_after();
+          if (PASS == 2) issue_group_b(it, acc);
+          commit(&bars->s_full[stage]);
+          commit(&bars->strm_free[it % C::NSLOT]);
+          PROF_MARK(2)
+        }
+      } else {
+        const uint32_t acc = tmem_base + C::OUT_COLS;
+        const uint32_t out0 = tmem_base, out1 = tmem_base + D;
+        ok = ok && issue_group_a(0, acc);
+        if (ok) {
+          commit(&bars->s_full[0]);
+          issue_group_b(0, acc);
+          commit(&bars->s_full[1]);
+        }
+        PROF_MARK(2)
+        for (int it = 0; ok && it < n_iter; ++it) {
+          const uint32_t sl = strm_lo + (it % C::NSLOT) * kSlot16;
           const bool accum = it > 0;
-          const uint32_t out0 = tmem_base, out1 = tmem_base + D;
-          gemm_ts<D, BN>(out0, acc + 2 * BN, sr(1), idesc_o, accum);  // dS  . ddK | ddQ
-          gemm_ts<D, BN>(out0, acc + 3 * BN, sr(0), idesc_o, true);   // dS2 . K   | Q
-          gemm_ts<D, BN>(out1, acc + 1 * BN, sr(2), idesc_o, accum);  // ddP . V   | dO
-          if (kQStat) gemm_ts<D, BN>(out1, acc + 0 * BN, sr(3), idesc_o, true);  // P . ddV
-          umma_commit(&bars->strm_free[slot]);
+          // outputs fed by group A (P, ddP live where S, A2 were)
+          PROF_MARK(7)
+          ok = wait_all(&bars->p_full[0], it & 1);
+          if (!ok) break;
+          PROF_MARK(3)
+          tc_fence_after();
+          gemm_ts<D, BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o, accum);              // ddP . V | dO
+          if (kQStat) gemm_ts<D, BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o, true);   // P . ddV
+          // group A of the next tile may overwrite S/A2 now: the MMAs above were issued first
+          if (it + 1 < n_iter) {
+            ok = issue_group_a(it + 1, acc);
+            if (!ok) break;
+            commit(&bars->s_full[0]);
+          }
+          PROF_MARK(4)
+          // outputs fed by group B (dS, dS2 live where dP, X were)
+          ok = wait_all(&bars->p_full[1], it & 1);
+          if (!ok) break;
+          PROF_MARK(5)
+          tc_fence_after();
+          gemm_ts<D, BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o, accum);  // dS  . ddK | ddQ
+          gemm_ts<D, BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o, true);   // dS2 . K   | Q
+          commit(&bars->strm_free[it % C::NSLOT]);
+          if (it + 1 < n_iter) {
+            issue_group_b(it + 1, acc);
+            commit(&bars->s_full[1]);
+          }
+          PROF_MARK(6)
         }
       }
+#ifdef FHOB_TC_PROFILE
+      if (leader) PROF_FLUSH(8)
+#endif
       if (ok) {
-        umma_commit(&bars->out_full);
+        commit(&bars->out_full);
       } else {
         // abort path: no tcgen05.mma may still be reading shared memory or TMEM at exit
-        umma_commit(&bars->teardown);
+        commit(&bars->teardown);
         const long long start = clock64();
         while (!mbar_try_wait(&bars->teardown, 0)) {
           if (clock64() - start > kTimeoutCycles) break;
@@ -302,149 +559,108 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     }
   } else {
     // ================================================= elementwise warps
-    const int quad = warp & 3, half = warp >> 2;
+    const int quad = warp & 3, half = (warp - EW_WARP0) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int g_row = m0 + row;  // stationary row of this thread
     const size_t vec_head = static_cast<size_t>(head) * p.n_q;
-    const float scale = p.scale, sl2 = p.scale * kLog2e;
-
-    float r_nlc = 0.f, r_nds = 0.f, r_ndd = 0.f, r_nbs = 0.f;
+    EwCtx c;
+    c.scale = p.scale;
+    c.sl2 = p.scale * kLog2e;
+    c.r_nlc = c.r_k1 = c.r_ndd = c.r_k23 = 0.f;
     if (kQStat && g_row < p.n_q) {
-      r_nlc = p.nlc[vec_head + g_row];
+      c.r_nlc = p.nlc[vec_head + g_row];
       if (PASS >= 2) {
-        r_nds = p.nds[vec_head + g_row];
-        r_ndd = p.ndd[vec_head + g_row];
+        c.r_k1 = p.k1[vec_head + g_row];
+        c.r_ndd = p.ndd[vec_head + g_row];
       }
-      if (PASS >= 3) r_nbs = p.nbs[vec_head + g_row];
+      if (PASS >= 3) c.r_k23 = p.k23[vec_head + g_row];
     }
-    // visible streamed index range of this thread's row: lo <= idx <= hi
-    int lo, hi;
+    c.sv = 0;
     if (kQStat) {
-      lo = 0;
-      hi = p.n_k - 1;
-      if (p.causal && g_row + off < hi) hi = g_row + off;
+      c.lo = 0;
+      c.hi = p.n_k - 1;
+      if (p.causal && g_row + off < c.hi) c.hi = g_row + off;
     } else {
-      lo = p.causal ? g_row - off : 0;
-      if (lo < 0) lo = 0;
-      hi = p.n_q - 1;
+      c.lo = p.causal ? g_row - off : 0;
+      if (c.lo < 0) c.lo = 0;
+      c.hi = p.n_q - 1;
     }
     float rowacc = 0.f;
     bool ok = true;
+    PROF_DECL
 
     for (int it = 0; it < n_iter; ++it) {
-      const int stage = it % C::NSS;
       const int n0 = (t_begin + it) * BN;
-      ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[stage], (it / C::NSS) & 1, bars, p.status));
-      if (!ok) break;
-      tc_fence_after();
-      // does any element of this tile need masking?  (warp-uniform: depends on tile coordinates only)
+      // does any element of this tile need masking?  (CTA-uniform: depends on tile coordinates only)
       bool masked = n0 + BN > n_strm;
       if (p.causal) {
         if (kQStat) masked = masked || (n0 + BN - 1 > m0 + off);
         else masked = masked || (n0 + off < m0 + BM - 1);
       }
-      const uint32_t acc = tmem_base + lane_base + C::OUT_COLS + stage * C::STAGE_COLS + half * (BN / 2);
-#pragma unroll
-      for (int c = 0; c < C::CH; ++c) {
-        const int col0 = n0 + half * (BN / 2) + 16 * c;  // streamed index of this chunk's first column
-        uint32_t s[16], a2[16], dp[16], x[16];
-        tmem_ld16(acc + 0 * BN + 16 * c, s);
-        tmem_ld16(acc + 1 * BN + 16 * c, a2);
-        if (PASS >= 2) {
-          tmem_ld16(acc + 2 * BN + 16 * c, dp);
-          tmem_ld16(acc + 3 * BN + 16 * c, x);
-        }
-        tmem_wait_ld();
-        uint32_t w_ds[8], w_ds2[8], w_ddp[8], w_p[8];
-#pragma unroll
-        for (int j4 = 0; j4 < 4; ++j4) {
-          float c_nlc[4], c_nds[4], c_ndd[4], c_nbs[4];
-          if (kQStat) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) { c_nlc[e] = r_nlc; c_nds[e] = r_nds; c_ndd[e] = r_ndd; c_nbs[e] = r_nbs; }
-          } else {
-            const size_t vi = vec_head + col0 + 4 * j4;
-            float4 v0 = __ldg(reinterpret_cast<const float4*>(p.nlc + vi));
-            float4 v1 = __ldg(reinterpret_cast<const float4*>(p.nds + vi));
-            float4 v2 = __ldg(reinterpret_cast<const float4*>(p.ndd + vi));
-            float4 v3 = __ldg(reinterpret_cast<const float4*>(p.nbs + vi));
-            c_nlc[0] = v0.x; c_nlc[1] = v0.y; c_nlc[2] = v0.z; c_nlc[3] = v0.w;
-            c_nds[0] = v1.x; c_nds[1] = v1.y; c_nds[2] = v1.z; c_nds[3] = v1.w;
-            c_ndd[0] = v2.x; c_ndd[1] = v2.y; c_ndd[2] = v2.z; c_ndd[3] = v2.w;
-            c_nbs[0] = v3.x; c_nbs[1] = v3.y; c_nbs[2] = v3.z; c_nbs[3] = v3.w;
-          }
-          float o_ds[4], o_ds2[4], o_ddp[4], o_p[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int j = 4 * j4 + e;
-            const float fs = __uint_as_float(s[j]), fa2 = __uint_as_float(a2[j]);
-            bool allowed = true;
-            if (masked) {
-              const int idx = col0 + j;
-              allowed = idx >= lo && idx <= hi;
-            }
-            float pr = ex2(fmaf(fs, sl2, c_nlc[e]));
-            if (masked) pr = allowed ? pr : 0.f;
-            if (PASS == 1) {
-              rowacc = fmaf(pr, fa2, rowacc);
-            } else {
-              const float fdp = __uint_as_float(dp[j]), fx = __uint_as_float(x[j]);
-              const float tt = fmaf(fa2, scale, c_ndd[e]);
-              float u = fmaf(fdp, tt, fx);
-              u = fmaf(c_nds[e], fa2, u);
-              if (PASS == 2) {
-                float term = pr * u;
-                if (masked) term = allowed ? term : 0.f;
-                rowacc += term;
-              } else {
-                o_ds[e] = pr * fmaf(fdp, scale, c_nds[e]);
-                o_ds2[e] = pr * fmaf(u, scale, c_nbs[e]);
-                o_ddp[e] = pr * tt;
-                o_p[e] = pr;
-                if (masked && !allowed) { o_ds[e] = 0.f; o_ds2[e] = 0.f; o_ddp[e] = 0.f; }
-              }
-            }
-          }
-          if (PASS >= 3) {
-            w_ds[2 * j4] = pack_bf16(o_ds[0], o_ds[1]);
-            w_ds[2 * j4 + 1] = pack_bf16(o_ds[2], o_ds[3]);
-            w_ds2[2 * j4] = pack_bf16(o_ds2[0], o_ds2[1]);
-            w_ds2[2 * j4 + 1] = pack_bf16(o_ds2[2], o_ds2[3]);
-            w_ddp[2 * j4] = pack_bf16(o_ddp[0], o_ddp[1]);
-            w_ddp[2 * j4 + 1] = pack_bf16(o_ddp[2], o_ddp[3]);
-            if (PASS == 3) {
-              w_p[2 * j4] = pack_bf16(o_p[0], o_p[1]);
-              w_p[2 * j4 + 1] = pack_bf16(o_p[2], o_p[3]);
-            }
-          }
-        }
-        if (PASS >= 3) {
-          // bf16 tiles overwrite the accumulator columns this thread has already consumed
-          tmem_st8(acc + 2 * BN + 8 * c, w_ds);
-          tmem_st8(acc + 3 * BN + 8 * c, w_ds2);
-          tmem_st8(acc + 1 * BN + 8 * c, w_ddp);
-          if (PASS == 3) tmem_st8(acc + 0 * BN + 8 * c, w_p);
-        }
-      }
-      if (PASS <= 2) {
+      const int col_base = n0 + half * (BN / 2);
+      if constexpr (PASS <= 2) {
+        const int stage = it % C::NSS;
+        PROF_MARK(7)
+        ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[stage], (it / C::NSS) & 1, bars, p.status));
+        if (!ok) break;
+        PROF_MARK(0)
+        tc_fence_after();
+        const uint32_t acc = tmem_base + lane_base + stage * C::STAGE_COLS + half * (BN / 2);
+        if (masked) ew_reduce<PASS, BN, true>(acc, col_base, c, rowacc);
+        else ew_reduce<PASS, BN, false>(acc, col_base, c, rowacc);
+        PROF_MARK(1)
         tc_fence_before();
         mbar_arrive(&bars->s_free[stage]);
+        PROF_MARK(2)
       } else {
+        const uint32_t acc = tmem_base + lane_base + C::OUT_COLS + half * (BN / 2);
+        float2 ps[16], tt[16];
+        if (PASS == 4) {
+          // the slot's constants were written by the TMA unit: observe its barrier before reading them
+          const int slot = it % C::NSLOT;
+          ok = __all_sync(0xffffffffu, wait_bar(&bars->strm_full[slot], (it / C::NSLOT) & 1, bars, p.status));
+          if (!ok) break;
+          c.sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::NSTRM * C::STRM_BYTES);
+        }
+        PROF_MARK(7)
+        ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[0], it & 1, bars, p.status));
+        if (!ok) break;
+        PROF_MARK(0)
+        tc_fence_after();
+        if (masked) ew_half_a<PASS, true>(acc, col_base, half * (BN / 2), c, ps, tt);
+        else ew_half_a<PASS, false>(acc, col_base, half * (BN / 2), c, ps, tt);
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(&bars->p_full);
+        mbar_arrive(&bars->p_full[0]);
+        PROF_MARK(1)
+        ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[1], it & 1, bars, p.status));
+        if (!ok) break;
+        PROF_MARK(4)
+        tc_fence_after();
+        if (masked) ew_half_b<PASS, true>(acc, col_base, half * (BN / 2), c, ps, tt);
+        else ew_half_b<PASS, false>(acc, col_base, half * (BN / 2), c, ps, tt);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[1]);
+        PROF_MARK(2)
       }
     }
+#ifdef FHOB_TC_PROFILE
+    if (threadIdx.x == EW_WARP0 * 32) {
+      prof_t[3] = n_iter;
+      PROF_FLUSH(0)
+    }
+#endif
 
     // ---- results
     if (PASS <= 2) {
       if (half == 1) bars->red[row] = rowacc;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (half == 0 && ok && g_row < p.n_q) {
-        float tot = rowacc + bars->red[row];
-        if (PASS == 1) p.ndd[vec_head + g_row] = -scale * tot;
-        else p.nbs[vec_head + g_row] = -scale * tot;
+        const float tot = rowacc + bars->red[row];
+        if (PASS == 1) p.ndd[vec_head + g_row] = -c.scale * tot;     // -dd, dd = scale * sum P A2
+        else p.k23[vec_head + g_row] = -c.r_k1 * c.r_ndd - tot;      // -D*dd - b, b = sum P dP2
       }
     } else {
       if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, p.status));
@@ -455,10 +671,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           __nv_bfloat16* dst = (o == 0 ? p.out0 : p.out1) +
                                (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
+          for (int ch = 0; ch < D / 32; ++ch) {
             uint32_t v[16];
             if (n_iter > 0) {
-              tmem_ld16(tmem_base + lane_base + o * D + half * (D / 2) + 16 * c, v);
+              tmem_ld16(tmem_base + lane_base + o * D + half * (D / 2) + 16 * ch, v);
               tmem_wait_ld();
             } else {
 #pragma unroll
@@ -474,7 +690,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
               w1.y = pack_bf16(__uint_as_float(v[10]), __uint_as_float(v[11]));
               w1.z = pack_bf16(__uint_as_float(v[12]), __uint_as_float(v[13]));
               w1.w = pack_bf16(__uint_as_float(v[14]), __uint_as_float(v[15]));
-              uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * c);
+              uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
               d4[0] = w0;
               d4[1] = w1;
             }
@@ -533,6 +749,13 @@ int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows) {
   return FHOB_OK;
 }
 
+// Streamed-tile height of pass 1 (the other passes use 64 rows).  128 rows let the stacked
+// [K ; ddK] operand reach N = 256; FHOB_TC_BN1=64 selects the smaller tile for experiments.
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return v ? atoi(v) : dflt;
+}
+
 template <int PASS, int D, int BN>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, D, BN>;
@@ -550,7 +773,7 @@ int launch(const FhobProblem& p, cudaStream_t s) {
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, BN);
   }
   if (st != FHOB_OK) return st;
-  tp.nlc = rv.nlc; tp.nds = rv.nds; tp.ndd = rv.ndd; tp.nbs = rv.nbs;
+  tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
   tp.out0 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.dq2 : p.dk2);
   tp.out1 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.ddo : p.dv2);
   tp.status = rv.status;
@@ -561,15 +784,35 @@ int launch(const FhobProblem& p, cudaStream_t s) {
                                     C::SMEM_BYTES));
   const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
   if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
+#ifdef FHOB_TC_PROFILE
+  static unsigned long long* prof_dev = nullptr;
+  if (!prof_dev) FHOB_CUDA_OK(cudaMalloc(&prof_dev, 24 * sizeof(unsigned long long)));
+  FHOB_CUDA_OK(cudaMemsetAsync(prof_dev, 0, 24 * sizeof(unsigned long long), s));
+  tp.prof = prof_dev;
+#endif
   tc_pass_kernel<PASS, D, BN><<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
   FHOB_CUDA_OK(cudaGetLastError());
+#ifdef FHOB_TC_PROFILE
+  if (getenv("FHOB_TC_PROF_PRINT")) {
+    unsigned long long h[24];
+    FHOB_CUDA_OK(cudaMemcpyAsync(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost, s));
+    FHOB_CUDA_OK(cudaStreamSynchronize(s));
+    const double it = h[3] > 0 ? static_cast<double>(h[3]) : 1.0;  // tile iterations summed over CTAs
+    fprintf(stderr, "[prof] pass %d D %d BN %d cycles/tile-iter | EW:", PASS, D, BN);
+    for (int i = 0; i < 8; ++i) if (i != 3) fprintf(stderr, " e%d=%.0f", i, h[i] / it);
+    fprintf(stderr, " | MMA:");
+    for (int i = 0; i < 8; ++i) fprintf(stderr, " m%d=%.0f", i, h[8 + i] / it);
+    fprintf(stderr, " | TMA: wait_free=%.0f issue=%.0f other=%.0f\n", h[16] / it, h[17] / it, h[23] / it);
+  }
+#endif
   return FHOB_OK;
 }
 
 template <int D>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
+  static const int bn1 = env_int("FHOB_TC_BN1", 128);
   switch (pass) {
-    case 1: return launch<1, D, 64>(p, s);
+    case 1: return bn1 == 64 ? launch<1, D, 64>(p, s) : launch<1, D, 128>(p, s);
     case 2: return launch<2, D, 64>(p, s);
     case 3: return launch<3, D, 64>(p, s);
     case 4: return launch<4, D, 64>(p, s);

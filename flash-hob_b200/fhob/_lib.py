@@ -4,7 +4,10 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "libfhob.so"
+import os
+
+# FHOB_LIB_PATH points at an alternative build of the same library (e.g. an instrumented one)
+LIB_PATH = Path(os.environ.get("FHOB_LIB_PATH") or Path(__file__).resolve().parent / "libfhob.so")
 
 FHOB_BF16, FHOB_F32 = 0, 1
 IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
