@@ -48,9 +48,14 @@ WORKLOADS = {
                   desc="bf16 non-causal B=1 H=32 N=8192 D=128"),
 }
 GEMM_UNITS = {"pass1": 3, "pass2": 5, "pass3": 9, "pass4": 8}
-# dram__bytes_read.sum + dram__bytes_write.sum of one pass-3 launch, from the ncu capture summarised
-# in profiles/ (captured on a smaller head count and scaled by heads); None until captured.
-PASS3_DRAM_BYTES_PER_HEAD = None
+# dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass on the default
+# workload's shape (N_Q=4096, N_K=8192, D=128), from the ncu capture summarised in
+# profiles/tc_pass_kernels_cfg5_16heads.md (captured with 16 heads; traffic grows in proportion to
+# the heads, every head having its own tensors).  None for shapes that were not captured.
+DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass1"): 105.48e6 / 16, ("cfg5-shard", "pass2"): 190.34e6 / 16,
+                       ("cfg5-shard", "pass3"): 209.92e6 / 16, ("cfg5-shard", "pass4"): 229.08e6 / 16}
+KERNEL_NAMES = {"pass1": "tc_pass_kernel<1, {d}, 128>", "pass2": "tc_pass_kernel<2, {d}, 64>",
+                "pass3": "tc_pass_kernel<3, {d}, 64>", "pass4": "tc_pass_kernel<4, {d}, 64>"}
 
 
 def pairs(w):
@@ -165,6 +170,37 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def mem_sweep():
+    """Peak memory of one operator call against sequence length (bf16 causal, 2 heads, D=128).
+
+    Prints one JSON line: per length the bytes of the nine inputs, of the four outputs, the extra
+    bytes the call allocated beyond its outputs (the workspace) and what a dense fp32 score
+    matrix per head pair would have taken."""
+    import fhob
+    from fhob import ops
+    dev = torch.device("cuda", 0)
+    rows = []
+    for n in (2048, 4096, 8192, 16384, 32768, 65536):
+        w = dict(bh=2, n_q=n, n_k=n, d=128, causal=True, cot=1.0)
+        x = make_batch(w, dev, 7)
+        o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 128 ** -0.5, is_causal=True)
+        torch.cuda.synchronize()
+        ops._workspaces.clear()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats(dev)
+        base = torch.cuda.memory_allocated(dev)
+        outs = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 128 ** -0.5,
+                                 is_causal=True, check=True)
+        peak = torch.cuda.max_memory_allocated(dev) - base
+        out_bytes = sum(t.numel() * t.element_size() for t in outs)
+        in_bytes = sum(t.numel() * t.element_size() for t in list(x.values()) + [o, lse])
+        rows.append(dict(n=n, input_bytes=in_bytes, output_bytes=out_bytes, extra_bytes=peak - out_bytes,
+                         dense_fp32_scores_bytes=2 * n * n * 4))
+        del x, o, lse, outs
+    print(json.dumps(dict(mem_sweep=rows, note="extra_bytes = workspace (status word + 4 fp32 row vectors, "
+                          "1 MiB minimum block); grows linearly with n")), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -176,7 +212,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--heads", type=int, default=0, help="heads per GPU (default: the workload's); "
                     "smaller values give the small cases profiler captures need")
+    ap.add_argument("--mem-sweep", action="store_true",
+                    help="instead of the benchmark: peak device memory of one call vs sequence length")
     args = ap.parse_args()
+    if args.mem_sweep:
+        mem_sweep()
+        return
     w = dict(WORKLOADS[args.workload])
     if args.heads > 0:
         w["bh"] = args.heads
@@ -266,14 +307,17 @@ def main():
             tf = GEMM_UNITS[s] * unit_flops / (ms * 1e-3) / 1e12
             passes[s].update(tflops=round(tf, 1), frac_of_sustained_peak=round(tf / peaks["sustained"], 4))
     dom = max(GEMM_UNITS, key=lambda s: passes[s]["ms"])
-    roofline = dict(bound="tensor", kernel=f"tc_pass_kernel<{dom[-1]}, {w['d']}, 64>", achieved=passes[dom]["tflops"],
+    per_head = DRAM_BYTES_PER_HEAD.get((args.workload, dom))
+    for s in GEMM_UNITS:
+        ph = DRAM_BYTES_PER_HEAD.get((args.workload, s))
+        passes[s]["dram_traffic_bytes"] = ph * w["bh"] if ph else None
+    roofline = dict(bound="tensor", kernel=KERNEL_NAMES[dom].format(d=w["d"]), achieved=passes[dom]["tflops"],
                     peak=peaks["sustained"], unit="TFLOP/s",
                     frac=round(passes[dom]["tflops"] / peaks["sustained"], 4),
                     frac_of_burst_peak=round(passes[dom]["tflops"] / peaks["burst"], 4),
                     peak_source=f"{peaks['src']} cuBLAS bf16 (sustained, kernel timed inside a long step)",
                     flops_basis=f"{GEMM_UNITS[dom]} contractions of 2*BH*pairs*D flop issued by this pass",
-                    traffic=(PASS3_DRAM_BYTES_PER_HEAD * w["bh"] if PASS3_DRAM_BYTES_PER_HEAD and dom == "pass3"
-                             else None))
+                    traffic=per_head * w["bh"] if per_head else None)
 
     # ---- end to end through the public entry point with host buffers
     e2e = None
