@@ -137,13 +137,48 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    staged = [t.to(dev, non_blocking=True) for t in (Q, K, V, O, dO, ddQ, ddK, ddV, L)]
-    outs = _run_device(*staged, scale, is_causal, impl, check)
-    host = [torch.empty(o.shape, dtype=o.dtype, device="cpu", pin_memory=True) for o in outs]
-    for h, o in zip(host, outs):
-        h.copy_(o, non_blocking=True)
-    torch.cuda.current_stream(dev).synchronize()
-    return tuple(host)
+    return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev)
+
+
+_copy_streams: dict = {}
+
+
+def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8):
+    """Host tensors in, pinned host tensors out.  Heads are independent, so the batch is cut into
+    up to `max_chunks` head ranges that flow through three streams: upload of range i+1, the
+    kernels of range i and the download of range i-1 overlap."""
+    shape_q, shape_k = mats[0].shape, mats[1].shape
+    mats3 = [_fold(t, n) for t, n in zip(mats, ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV"))]
+    bh = mats3[0].shape[0]
+    lse = (L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)).to(torch.float32)
+    if lse.shape[0] != bh:
+        raise ValueError(f"L: expected {bh} rows, got {tuple(L.shape)}")
+    outs_host = [torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+                 for t in (mats3[0], mats3[1], mats3[1], mats3[0])]
+    main = torch.cuda.current_stream(dev)
+    up, down = _copy_streams.setdefault(dev.index, (torch.cuda.Stream(dev), torch.cuda.Stream(dev)))
+    up.wait_stream(main)
+    n_chunks = max(1, min(max_chunks, bh))
+    bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
+    for lo, hi in zip(bounds, bounds[1:]):
+        with torch.cuda.stream(up):
+            staged = [t[lo:hi].to(dev, non_blocking=True) for t in mats3 + [lse]]
+            ready = torch.cuda.Event()
+            ready.record(up)
+        main.wait_event(ready)
+        for t in staged:
+            t.record_stream(main)
+        res = _run_device(*staged, scale, is_causal, impl, check)  # check=True synchronises per range
+        done = torch.cuda.Event()
+        done.record(main)
+        down.wait_event(done)
+        with torch.cuda.stream(down):
+            for h, r in zip(outs_host, res):
+                r.record_stream(down)
+                h[lo:hi].copy_(r.reshape(h[lo:hi].shape), non_blocking=True)
+    down.synchronize()
+    return (outs_host[0].reshape(shape_q), outs_host[1].reshape(shape_k), outs_host[2].reshape(shape_k),
+            outs_host[3].reshape(shape_q))
 
 
 def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False):
