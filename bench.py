@@ -78,8 +78,12 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi.
+
+    The process is started well before the timed region (its start-up touches the driver) and
+    keeps sampling every 50 ms; `window(t0, t1)` then summarises only the samples whose
+    timestamps fall inside the timed region."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
@@ -92,7 +96,9 @@ class ClockSampler:
         except OSError:
             pass
 
-    def stop(self):
+    def window(self, t0, t1):
+        """Stops sampling; t0/t1 are time.time() stamps bracketing the timed region."""
+        import datetime
         if self.proc is None:
             return None
         self.proc.terminate()
@@ -101,27 +107,30 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        clocks, max_clk, reasons = [], None, set()
+        clocks, powers, max_clk, reasons, total = [], [], None, set(), 0
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
         for line in out.strip().splitlines():
             f = [s.strip() for s in line.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
+            total += 1
             try:
-                clocks.append(float(f[0]))
-                max_clk = float(f[1])
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, mx, pw = float(f[1]), float(f[2]), float(f[3])
             except ValueError:
                 continue
-            for n, v in zip(names, f[3:7]):
+            if not (t0 - 0.03 <= ts <= t1 + 0.03):
+                continue
+            clocks.append(clk)
+            powers.append(pw)
+            max_clk = mx
+            for n, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         if not clocks:
-            return None
-        # the first samples can predate the load: take the median of the upper half
-        clocks.sort()
-        upper = clocks[len(clocks) // 2:]
-        return dict(sm_mhz=statistics.median(upper), sm_max_mhz=max_clk, reasons=sorted(reasons),
-                    samples=len(clocks))
+            return dict(sm_mhz=None, sm_max_mhz=max_clk, reasons=[], samples=0, samples_total=total)
+        return dict(sm_mhz=statistics.median(clocks), sm_max_mhz=max_clk, power_w_median=statistics.median(powers),
+                    reasons=sorted(reasons), samples=len(clocks), samples_total=total)
 
 
 def make_batch(w, device, seed):
@@ -210,6 +219,7 @@ def main():
     ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
     ap.add_argument("--heads", type=int, default=0, help="heads per GPU (default: the workload's); "
                     "smaller values give the small cases profiler captures need")
     ap.add_argument("--mem-sweep", action="store_true",
@@ -264,18 +274,32 @@ def main():
         return fhob.flash_bwdbwd(*args_dev, is_causal=w["causal"])
 
     # ---- device-resident timing
-    for _ in range(warmup):
-        step()
+    sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
+    if sampler:
+        time.sleep(0.5)   # let the sampler finish starting up outside the timed region
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    # warm-up: at least `warmup` steps and at least 0.3 s of work, so that the timed region starts
+    # with the clocks already up (an idle GPU needs tens of milliseconds to leave its idle clocks)
+    t_w = time.time()
+    done_w = 0
+    outs = None
+    while done_w < warmup or time.time() - t_w < 0.3:
+        outs = step()   # same allocation pattern as the timed loop: no cudaMalloc is left for it
+        done_w += 1
+        if done_w % 4 == 0:
+            torch.cuda.synchronize()
+    warmup = done_w
+    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_start = time.time()
     e0.record()
     for _ in range(args.steps):
         outs = step()
     e1.record()
     barrier()
+    t_end = time.time()
     ms_total = max_over_ranks(e0.elapsed_time(e1))
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.window(t_start, t_end) if sampler else None
     ms_step = ms_total / args.steps
     prob = _Problem(*args_dev, w["causal"], "auto")
     status = prob.status()

@@ -119,6 +119,7 @@ const char* fhob_strerror(int status) {
   }
   if (status & FHOB_ERR_TIMEOUT) return "device: a bounded wait ran out of iterations (results are invalid)";
   if (status & FHOB_ERR_SMEM_ALIGN) return "device: shared memory base not 1024-byte aligned";
+  if (status & FHOB_ERR_TMEM_BASE) return "device: tensor memory allocation did not start at column 0 (results are invalid)";
   return "unknown status";
 }
 

@@ -173,24 +173,26 @@ __device__ __forceinline__ constexpr uint32_t umma_desc_hi_sw128(uint32_t sbo_by
 __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
   return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
+// `issue` selects the one lane that issues; the other lanes of the warp execute the instruction
+// predicated off, so the call can sit in warp-uniform code.
 __device__ __forceinline__ void umma_ss_split(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
-                                              uint32_t idesc, uint32_t accumulate) {
+                                              uint32_t idesc, uint32_t accumulate, bool issue = true) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
       "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 __device__ __forceinline__ void umma_ts_split(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t hi,
-                                              uint32_t idesc, uint32_t accumulate) {
+                                              uint32_t idesc, uint32_t accumulate, bool issue = true) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 db;\n\t"
       "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate), "r"(static_cast<uint32_t>(issue))
       : "memory");
 }
 // Arrives on `bar` once every tcgen05.mma this thread issued so far has completed.

@@ -162,7 +162,7 @@ __device__ __forceinline__ void gemm_ss(bool leader, uint32_t d_tmem, uint32_t a
   for (int ks = 0; ks < D / 16; ++ks) {
     const uint32_t a = a_lo + (((ks / 4) * A_BOX + (ks % 4) * 32) >> 4);
     const uint32_t b = b_lo + (((ks / 4) * B_BOX + (ks % 4) * 32) >> 4);
-    if (leader) umma_ss_split(d_tmem, a, b, kDescHi, idesc, (accumulate || ks > 0) ? 1u : 0u);
+    umma_ss_split(d_tmem, a, b, kDescHi, idesc, (accumulate || ks > 0) ? 1u : 0u, leader);
   }
 }
 
@@ -176,7 +176,7 @@ __device__ __forceinline__ void gemm_ts(bool leader, uint32_t d_tmem, uint32_t a
 #pragma unroll
   for (int s = 0; s < BN / 16; ++s) {
     const uint32_t a = a_region + (s / CH) * (BN / 2) + 8 * (s % CH);
-    if (leader) umma_ts_split(d_tmem, a, b_lo + ((s * 2048) >> 4), kDescHi, idesc, (accumulate || s > 0) ? 1u : 0u);
+    umma_ts_split(d_tmem, a, b_lo + ((s * 2048) >> 4), kDescHi, idesc, (accumulate || s > 0) ? 1u : 0u, leader);
   }
 }
 
@@ -386,7 +386,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  // The CTA allocates all 512 columns, so the allocation starts at lane 0, column 0.  Using the
+  // constant keeps every TMEM address of the MMA issue loop an immediate; a different answer from
+  // the allocator is reported through the status word.
+  constexpr uint32_t tmem_base = 0;
+  if (threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base) != 0)
+    atomicOr(p.status, FHOB_ERR_TMEM_BASE);
 
   if (warp == TMA_WARP) {
     // ================================================= TMA producer

@@ -47,7 +47,8 @@ enum {
   FHOB_ERR_ARCH = 6,       /* tensor-core kernels need compute capability 10.x */
   FHOB_ERR_STATIC_LIMIT = 7, /* fhob_bwdbwd_static_scratch: bh*n_q exceeds FHOB_STATIC_SCRATCH_MAX_ROWS */
   FHOB_ERR_TIMEOUT = 64,   /* device: a bounded mbarrier wait ran out (bit in the status word) */
-  FHOB_ERR_SMEM_ALIGN = 128 /* device: dynamic shared memory base was not 1024-byte aligned */
+  FHOB_ERR_SMEM_ALIGN = 128, /* device: dynamic shared memory base was not 1024-byte aligned */
+  FHOB_ERR_TMEM_BASE = 256   /* device: the tensor-memory allocation did not start at column 0 */
 };
 
 /*
