@@ -54,16 +54,16 @@ __global__ void row_stats_kernel(const float* k1, const float* ndd, const float*
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int validate(const FhobProblem* p, bool need_outputs) {
+int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = true) {
   if (!p) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0) return FHOB_ERR_ARG;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
   if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
   if (p->causal != 0 && p->causal != 1) return FHOB_ERR_ARG;
-  const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->ddq, p->ddk, p->ddv, p->lse};
-  for (const void* x : ins) {
-    if (!x) return FHOB_ERR_ARG;
-    if (!aligned16(x)) return FHOB_ERR_ALIGN;
+  const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->lse, p->ddq, p->ddk, p->ddv};
+  for (int i = 0; i < (need_cotangents ? 9 : 6); ++i) {
+    if (!ins[i]) return FHOB_ERR_ARG;
+    if (!aligned16(ins[i])) return FHOB_ERR_ALIGN;
   }
   if (need_outputs) {
     const void* outs[] = {p->dq2, p->dk2, p->dv2, p->ddo};
@@ -132,9 +132,7 @@ size_t fhob_workspace_bytes(int32_t bh, int32_t n_q) {
   return kWorkspaceHeaderBytes + 4 * rows * sizeof(float) + kWorkspaceTailBytes;
 }
 
-int fhob_prepass(const FhobProblem* p, void* stream) {
-  int st = validate(p, false);
-  if (st != FHOB_OK) return st;
+static int run_prepass(const FhobProblem* p, void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   RowVectors rv = row_vectors(*p);
   long rows = static_cast<long>(p->bh) * p->n_q;
@@ -151,6 +149,12 @@ int fhob_prepass(const FhobProblem* p, void* stream) {
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
+}
+
+int fhob_prepass(const FhobProblem* p, void* stream) {
+  int st = validate(p, false);
+  if (st != FHOB_OK) return st;
+  return run_prepass(p, stream);
 }
 
 int fhob_pass1(const FhobProblem* p, void* stream) { return run_pass(1, p, stream); }
@@ -198,6 +202,16 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
   return simt_forward(*p, o_out, lse_out, static_cast<cudaStream_t>(stream));
+}
+
+int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stream) {
+  if (!dq || !dk || !dv) return FHOB_ERR_ARG;
+  int st = validate(p, false, false);
+  if (st != FHOB_OK) return st;
+  if (!aligned16(dq) || !aligned16(dk) || !aligned16(dv)) return FHOB_ERR_ALIGN;
+  st = run_prepass(p, stream);  // stores -L*log2(e) and -D in the workspace
+  if (st != FHOB_OK) return st;
+  return simt_backward(*p, dq, dk, dv, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -66,6 +66,7 @@ void set_cuda_error_text(const char* text);
 // CUDA-core kernels (fp32 accumulate, any sizes): simt_kernels.cu
 int simt_pass(int pass, const FhobProblem& p, cudaStream_t s);
 int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s);
+int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s);
 
 // tcgen05 / TMEM / TMA kernels (bf16, d in {64,128}): tc_kernels.cu
 bool tc_supported(const FhobProblem& p);

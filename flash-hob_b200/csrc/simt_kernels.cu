@@ -382,6 +382,136 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
   }
 }
 
+// First backward (dQ | dK, dV) of attention from the saved forward results, O(N) memory.
+// KSIDE = false: a CTA owns TM queries and streams keys:   dQ = scale * (P (dP - D)) K.
+// KSIDE = true:  a CTA owns TM keys and streams queries:   dV = P^T dO,  dK = scale * (P (dP - D))^T Q.
+// Reads nlc = -L*log2(e) and k1 = -D from the workspace (written by the pre-pass).
+template <typename T, bool KSIDE>
+__global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, void* out0, void* out1) {
+  extern __shared__ float smem[];
+  const int d = p.d, ld = d + 1;
+  float* stat0 = smem;                       // Q | K
+  float* stat1 = stat0 + TM * ld;            // dO | V
+  float* strm0 = stat1 + TM * ld;            // K | Q
+  float* strm1 = strm0 + TN * ld;            // V | dO
+  float* pt = strm1 + TN * ld;               // [2][TM][TN+1]: P and dS tiles
+  float* svec = pt + 2 * TM * (TN + 1);      // [2][TN]: nlc, k1 of streamed queries (KSIDE)
+  constexpr int LT = TN + 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * TM, bh = blockIdx.y;
+  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
+  const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
+  const size_t voff = static_cast<size_t>(bh) * p.n_q;
+  const int causal_off = p.n_k - p.n_q;
+  const int n_stat = KSIDE ? p.n_k : p.n_q, n_strm = KSIDE ? p.n_q : p.n_k;
+  if (KSIDE) {
+    load_tile<T>(stat0, ld, p.k, koff, m0, TM, p.n_k, d);
+    load_tile<T>(stat1, ld, p.v, koff, m0, TM, p.n_k, d);
+  } else {
+    load_tile<T>(stat0, ld, p.q, qoff, m0, TM, p.n_q, d);
+    load_tile<T>(stat1, ld, p.d_o, qoff, m0, TM, p.n_q, d);
+  }
+  float r_nlc[RPW], r_k1[RPW];
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) {
+    const int qi = m0 + warp * RPW + i;
+    const bool ok = !KSIDE && qi < p.n_q;
+    r_nlc[i] = ok ? p.nlc[voff + qi] : 0.f;
+    r_k1[i] = ok ? p.k1[voff + qi] : 0.f;
+  }
+  float acc0[RPW][DCH], acc1[RPW][DCH];
+#pragma unroll
+  for (int i = 0; i < RPW; ++i)
+#pragma unroll
+    for (int m = 0; m < DCH; ++m) acc0[i][m] = acc1[i][m] = 0.f;
+  int t_begin = 0, t_end = (n_strm + TN - 1) / TN;
+  if (p.causal) {
+    if (!KSIDE) {
+      long last_key = static_cast<long>(m0) + TM - 1 + causal_off;
+      if (last_key < 0) t_end = 0;
+      else if (last_key / TN + 1 < t_end) t_end = static_cast<int>(last_key / TN + 1);
+    } else {
+      long first_q = static_cast<long>(m0) - causal_off;
+      if (first_q > 0) t_begin = static_cast<int>(first_q / TN);
+    }
+  }
+  const float sl2 = p.scale * kLog2e;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int n0 = t * TN;
+    __syncthreads();
+    if (KSIDE) {
+      load_tile<T>(strm0, ld, p.q, qoff, n0, TN, p.n_q, d);
+      load_tile<T>(strm1, ld, p.d_o, qoff, n0, TN, p.n_q, d);
+      if (threadIdx.x < TN) {
+        const int qi = n0 + threadIdx.x;
+        svec[threadIdx.x] = qi < p.n_q ? p.nlc[voff + qi] : 0.f;
+        svec[TN + threadIdx.x] = qi < p.n_q ? p.k1[voff + qi] : 0.f;
+      }
+    } else {
+      load_tile<T>(strm0, ld, p.k, koff, n0, TN, p.n_k, d);
+      load_tile<T>(strm1, ld, p.v, koff, n0, TN, p.n_k, d);
+    }
+    __syncthreads();
+    float s[RPW], dp[RPW];
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) s[i] = dp[i] = 0.f;
+    for (int e = 0; e < d; ++e) {
+      const float c0 = strm0[lane * ld + e], c1 = strm1[lane * ld + e];
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) {
+        const int r = warp * RPW + i;
+        s[i] = fmaf(stat0[r * ld + e], c0, s[i]);
+        dp[i] = fmaf(stat1[r * ld + e], c1, dp[i]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < RPW; ++i) {
+      const int r = warp * RPW + i;
+      const int qi = KSIDE ? n0 + lane : m0 + r, kj = KSIDE ? m0 + r : n0 + lane;
+      const bool allowed = qi < p.n_q && kj < p.n_k && (!p.causal || qi + causal_off >= kj);
+      const float nlc = KSIDE ? svec[lane] : r_nlc[i], k1 = KSIDE ? svec[TN + lane] : r_k1[i];
+      const float pr = allowed ? exp2f(fmaf(s[i], sl2, nlc)) : 0.f;
+      pt[(0 * TM + r) * LT + lane] = pr;
+      pt[(1 * TM + r) * LT + lane] = allowed ? pr * (dp[i] + k1) * p.scale : 0.f;  // dS
+    }
+    __syncwarp();
+    for (int c = 0; c < TN; ++c) {
+      float b0[DCH], b1[DCH];
+#pragma unroll
+      for (int m = 0; m < DCH; ++m) {
+        const int col = lane + 32 * m;
+        b0[m] = col < d ? strm0[c * ld + col] : 0.f;   // K | Q
+        b1[m] = col < d ? strm1[c * ld + col] : 0.f;   // V | dO
+      }
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) {
+        const int r = warp * RPW + i;
+        const float vp = pt[(0 * TM + r) * LT + c], vds = pt[(1 * TM + r) * LT + c];
+#pragma unroll
+        for (int m = 0; m < DCH; ++m) {
+          acc0[i][m] = fmaf(vds, b0[m], acc0[i][m]);              // dQ += dS K   | dK += dS^T Q
+          if (KSIDE) acc1[i][m] = fmaf(vp, b1[m], acc1[i][m]);    //              | dV += P^T dO
+        }
+      }
+    }
+  }
+  const size_t off = KSIDE ? koff : qoff;
+#pragma unroll
+  for (int i = 0; i < RPW; ++i) {
+    const int gr = m0 + warp * RPW + i;
+    if (gr >= n_stat) continue;
+#pragma unroll
+    for (int m = 0; m < DCH; ++m) {
+      const int col = lane + 32 * m;
+      if (col < d) {
+        st_elem<T>(out0, off + static_cast<size_t>(gr) * d + col, acc0[i][m]);
+        if (KSIDE) st_elem<T>(out1, off + static_cast<size_t>(gr) * d + col, acc1[i][m]);
+      }
+    }
+  }
+}
+
+
 size_t pass_smem_bytes(int d) {
   size_t ld = d + 1;
   return sizeof(float) * ((4 * TM + 4 * TN) * ld + 8 * TM * (TN + 1) + 4 * TN);
@@ -420,7 +550,28 @@ int dispatch_pass(int pass, const FhobProblem& p, cudaStream_t st) {
   return FHOB_ERR_ARG;
 }
 
+template <typename T>
+int launch_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t st) {
+  const size_t smem = sizeof(float) * ((2 * TM + 2 * TN) * (p.d + 1) + 2 * TM * (TN + 1) + 2 * TN);
+  SimtParams s = make_params(p);
+  FHOB_CUDA_OK(cudaFuncSetAttribute(simt_backward_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem)));
+  FHOB_CUDA_OK(cudaFuncSetAttribute(simt_backward_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem)));
+  simt_backward_kernel<T, false><<<dim3((p.n_q + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dq, nullptr);
+  FHOB_CUDA_OK(cudaGetLastError());
+  simt_backward_kernel<T, true><<<dim3((p.n_k + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dk, dv);
+  FHOB_CUDA_OK(cudaGetLastError());
+  return FHOB_OK;
+}
+
 }  // namespace
+
+int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t st) {
+  if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
+  return p.dtype == FHOB_F32 ? launch_backward<float>(p, dq, dk, dv, st)
+                             : launch_backward<__nv_bfloat16>(p, dq, dk, dv, st);
+}
 
 int simt_pass(int pass, const FhobProblem& p, cudaStream_t st) {
   if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;

@@ -193,10 +193,16 @@ __device__ __forceinline__ void load4(uint32_t smem_addr, float (&v)[4]) {
 
 // Passes 1 and 2: row reductions over one streamed tile.  acc = TMEM address of the stage (lane
 // and column-half offset included); col_base = streamed index of the thread's first column.
+__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) {
+  return make_float2(__uint_as_float(lo), __uint_as_float(hi));
+}
+
 template <int PASS, int BN, bool MASKED>
-__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float& rowacc) {
+__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float2& rowacc) {
   constexpr int CH = BN / 32;
-  const float nds = c.r_k1 * c.scale;  // -D*scale
+  const float2 sl2 = make_float2(c.sl2, c.sl2), nlc = make_float2(c.r_nlc, c.r_nlc);
+  const float2 scale = make_float2(c.scale, c.scale), ndd = make_float2(c.r_ndd, c.r_ndd);
+  const float2 nds = make_float2(c.r_k1 * c.scale, c.r_k1 * c.scale);  // -D*scale
 #pragma unroll
   for (int ch = 0; ch < CH; ++ch) {
     const int col0 = col_base + 16 * ch;
@@ -209,20 +215,22 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
     }
     tmem_wait_ld();
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const float fs = __uint_as_float(s[j]), fa2 = __uint_as_float(a2[j]);
-      float pr = ex2(fmaf(fs, c.sl2, c.r_nlc));
+    for (int j = 0; j < 16; j += 2) {  // two columns per packed fp32 instruction
+      const float2 fa2 = f2(a2[j], a2[j + 1]);
+      const float2 arg = __ffma2_rn(f2(s[j], s[j + 1]), sl2, nlc);
+      float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
       if (MASKED) {
         const int idx = col0 + j;
-        pr = (idx >= c.lo && idx <= c.hi) ? pr : 0.f;
+        pr.x = (idx >= c.lo && idx <= c.hi) ? pr.x : 0.f;
+        pr.y = (idx + 1 >= c.lo && idx + 1 <= c.hi) ? pr.y : 0.f;
       }
       if (PASS == 1) {
-        rowacc = fmaf(pr, fa2, rowacc);
+        rowacc = __ffma2_rn(pr, fa2, rowacc);
       } else {
-        const float tt = fmaf(fa2, c.scale, c.r_ndd);
-        float u = fmaf(__uint_as_float(dp[j]), tt, __uint_as_float(x[j]));
-        u = fmaf(nds, fa2, u);
-        rowacc = fmaf(pr, u, rowacc);
+        const float2 tt = __ffma2_rn(fa2, scale, ndd);
+        float2 u = __ffma2_rn(f2(dp[j], dp[j + 1]), tt, f2(x[j], x[j + 1]));
+        u = __ffma2_rn(nds, fa2, u);
+        rowacc = __ffma2_rn(pr, u, rowacc);
       }
     }
   }
@@ -230,12 +238,8 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
 
 // Passes 3 and 4 work on a thread's 32 columns of a 64-row streamed tile at once, two columns
 // per packed fp32 instruction (fma/mul/add .f32x2).
-__device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) {
-  return make_float2(__uint_as_float(lo), __uint_as_float(hi));
-}
-
 // First half of a tile: S, A2 -> P = exp2(S*sl2 + nlc), t = scale*A2 - dd; writes ddP = P t (and P
-// in pass 3) as bf16 over the accumulators and keeps P*scale and t in registers for the second half.
+// in pass 3) as bf16 over the accumulators and keeps P and t in registers for the second half.
 template <int PASS, bool MASKED>
 __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           float2 (&ps)[16], float2 (&tt)[16]) {
@@ -270,7 +274,7 @@ __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in
         t.x = ok0 ? t.x : 0.f;   t.y = ok1 ? t.y : 0.f;
       }
       const float2 ddp = __fmul2_rn(pr, t);
-      ps[j / 2] = __fmul2_rn(pr, scale);
+      ps[j / 2] = pr;
       tt[j / 2] = t;
       w_ddp[j / 2] = pack_bf16(ddp.x, ddp.y);
       if (PASS == 3) w_p[j / 2] = pack_bf16(pr.x, pr.y);
@@ -281,7 +285,8 @@ __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in
   if (PASS == 3) tmem_st16(acc + 0 * BN, w_p);
 }
 
-// Second half: dP' = dP - D, X' = X - D*dd - b, dS = (P scale) dP', dS2 = (P scale)(dP' t + X').
+// Second half: dP' = dP - D, X' = X - D*dd - b; writes P dP' and P (dP' t + X'), i.e. dS/scale and
+// dS2/scale: the factor `scale` is applied once to the finished dQ2 / dK2 accumulator instead.
 template <int PASS, bool MASKED>
 __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           const float2 (&ps)[16], const float2 (&tt)[16]) {
@@ -591,7 +596,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (c.lo < 0) c.lo = 0;
       c.hi = p.n_q - 1;
     }
-    float rowacc = 0.f;
+    float2 rowacc = make_float2(0.f, 0.f);
     bool ok = true;
     PROF_DECL
 
@@ -660,10 +665,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
     // ---- results
     if (PASS <= 2) {
-      if (half == 1) bars->red[row] = rowacc;
+      if (half == 1) bars->red[row] = rowacc.x + rowacc.y;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (half == 0 && ok && g_row < p.n_q) {
-        const float tot = rowacc + bars->red[row];
+        const float tot = rowacc.x + rowacc.y + bars->red[row];
         if (PASS == 1) p.ndd[vec_head + g_row] = -c.scale * tot;     // -dd, dd = scale * sum P A2
         else p.k23[vec_head + g_row] = -c.r_k1 * c.r_ndd - tot;      // -D*dd - b, b = sum P dP2
       }
@@ -684,6 +689,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = 0u;
+            }
+            if (o == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * c.scale);
             }
             if (g_row < n_stat) {
               uint4 w0, w1;

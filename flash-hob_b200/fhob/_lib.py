@@ -17,7 +17,7 @@ ERR_TIMEOUT, ERR_SMEM_ALIGN = 64, 128
 SYMBOLS = (
     "fhob_version", "fhob_strerror", "fhob_last_cuda_error", "fhob_workspace_bytes", "fhob_bwdbwd",
     "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
-    "fhob_read_status", "fhob_forward", "fhob_bwdbwd_static_scratch",
+    "fhob_read_status", "fhob_forward", "fhob_backward", "fhob_bwdbwd_static_scratch",
 )
 STATIC_SCRATCH_MAX_ROWS = 262144
 
@@ -60,6 +60,8 @@ def load() -> C.CDLL:
         fn.argtypes = [P, C.c_void_p]
     lib.fhob_row_stats.restype = C.c_int
     lib.fhob_row_stats.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.fhob_backward.restype = C.c_int
+    lib.fhob_backward.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fhob_forward.restype = C.c_int
     lib.fhob_forward.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p]
     _lib = lib

@@ -153,6 +153,17 @@ int fhob_read_status(const FhobProblem* p, void* stream);
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream);
 
 /*
+ * First backward of attention from the saved forward results, O(N) memory:
+ * dQ, dK, dV from q, k, v, o, d_o, lse (scale, causal) of `p`; the other
+ * cotangent pointers of `p` are ignored, the workspace is used (and
+ * overwritten).  Role of FlashAttention2.backward / flash_backward_torch in
+ * the reference (fhog/triton_flash.py:190-220), which materialises S, P, dP,
+ * dS.  It is the function whose derivative fhob_bwdbwd computes
+ * (jax_refs/flash_impl.py:124-173).  CUDA-core kernel.
+ */
+int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stream);
+
+/*
  * The operator for callers that cannot allocate device memory at all.
  * (No counterpart in the reference, whose wrapper allocates its temporaries
  * with torch on every call.)

@@ -268,3 +268,39 @@ def test_wrong_inputs_raise():
     q32 = torch.zeros(2, 128, 32, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="shape not supported"):
         fhob.flash_bwdbwd(q32, q32, q32, q32, q32, q32, q32, q32, L, 0.125, impl="tcgen05")
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)])
+def test_first_backward(dtype, tol, causal):
+    """fhob_backward against the oracle's attn_bwd (jax_refs/flash_impl.py:124-173)."""
+    import fhob
+    x = make_inputs(2, 200, 328, 64, seed=91, dtype=torch.float64)
+    ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], 0.125, causal)
+    o = O.attn_fwd(x["q"], x["k"], x["v"], 0.125, causal)
+    lse = O.attn_lse(x["q"], x["k"], 0.125, causal)
+    dev = {k: v.to(dtype).cuda() for k, v in x.items()}
+    got = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o.to(dtype).cuda(), dev["do"], lse.float().cuda(),
+                                  0.125, is_causal=causal)
+    for n, g, r in zip(("dq", "dk", "dv"), got, ref):
+        assert O.rel_err(g, r) < tol, n
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_autograd_grad_of_grad(causal):
+    """torch.autograd.grad twice through fhob.attention equals the oracle's grad-of-grad (form A):
+    the use the reference's commented-out Bwd function was meant for (fhog/triton_bwdbwd.py:538-554)."""
+    import fhob
+    x = make_inputs(2, 128, 256, 64, seed=93, dtype=torch.float64)
+    ref = O.bwdbwd_autograd(*x.values(), 0.125, causal)
+    ref_first = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], 0.125, causal)
+    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 3e-2)):
+        q, k, v, do = (x[n].to(dtype).cuda().requires_grad_(True) for n in ("q", "k", "v", "do"))
+        out = fhob.attention(q, k, v, 0.125, is_causal=causal)
+        dq, dk, dv = torch.autograd.grad(out, (q, k, v), do, create_graph=True)
+        for n, g, r in zip(("dq", "dk", "dv"), (dq, dk, dv), ref_first):
+            assert O.rel_err(g.detach(), r) < tol, (n, dtype)
+        cot = tuple(x[n].to(dtype).cuda() for n in ("ddq", "ddk", "ddv"))
+        got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
+        for n, g, r in zip(OUT_NAMES, got, ref):
+            assert O.rel_err(g, r) < tol, (n, dtype)
