@@ -72,9 +72,9 @@ struct Cfg {
   // Streamed tiles 2p and 2p+1 form a pair whose 64-column boxes interleave in shared memory
   // (box b of tile 2p, box b of tile 2p+1, box b+1 of tile 2p, ...), so that one K-major operand
   // descriptor can cover both tiles stacked as 2*BN rows: products that share their A operand
-  // (S and Q.ddK^T; dP and X) are then issued as one MMA with N = 2*BN.  Shared-memory operand
-  // bandwidth bounds an SS MMA at about 128 B/clk; N = 64 moves 6 KB per 32 tensor cycles and runs
-  // at half rate, N >= 128 runs at full rate.  An unpaired last tile keeps the compact layout.
+  // (S and Q.ddK^T; dP and X) are then issued as one MMA with N = 2*BN.  A tcgen05.mma occupies
+  // the tensor pipe for max(N/2, ~50) cycles on B200 (measured), so two N = 64 products cost 104
+  // cycles where one N = 128 product costs 64.  An unpaired last tile keeps the compact layout.
   __host__ __device__ static constexpr bool paired(int i) { return (i / 2) * 2 + 1 < NSTRM; }
   __host__ __device__ static constexpr int strm_base(int i) {
     return (i / 2) * 2 * STRM_BYTES + (paired(i) ? (i % 2) * BN * 128 : 0);
