@@ -16,9 +16,13 @@
 //     pass 3: ddO += ddP . V + P . ddV   (after group A)     dQ2 += dS . ddK + dS2 . K     (after group B)
 //     pass 4: dV2 += ddP^T . dO          (after group A)     dK2 += dS^T . ddQ + dS2^T . Q (after group B)
 //
-// Warp roles (320 threads): warp 0 = MMA issuer (one lane) and TMEM allocator, warp 1 = TMA
-// producer (one lane), warps 2-9 elementwise (warp w owns TMEM lanes 32*(w%4).., column half
-// (w-2)/4).
+// Warp roles (352 threads): warps 0 and 1 = MMA issuers (one lane each; warp 0 also allocates
+// TMEM), warp 2 = TMA producer (one lane), warps 3-10 elementwise (warp w owns TMEM lanes
+// 32*(w%4).., column half (w-3)/4).  The products of a tile fall into two chains that never touch
+// the same TMEM columns - chain 1: group A -> P, ddP -> ddO | dV2; chain 2: group B -> dS, dS2 ->
+// dQ2 | dK2 - so each chain has its own issuing warp, on its own warp scheduler.  Issuing a
+// tcgen05.mma keeps a thread busy for about 51 cycles and the elementwise warps of the same
+// scheduler delay it further; one thread cannot feed 64-cycle products under that load, two can.
 //   passes 1, 2: two score stages in TMEM; the MMA warp runs one tile ahead.
 //   passes 3, 4: TMEM is full with one stage (2*D + 4*64 columns), so the tile is pipelined in
 //   two halves instead: while the elementwise warps turn group A into P / ddP, the tensor core
@@ -41,10 +45,11 @@ using namespace ptx;
 
 constexpr int BM = 128;
 constexpr int EW_THREADS = 256;
-constexpr int MMA_WARP = 0;  // lowest warp id: the schedulers favour it over the elementwise warps
-constexpr int TMA_WARP = 1;
-constexpr int EW_WARP0 = 2;  // elementwise warps 2..9
-constexpr int NTHREADS = 320;
+constexpr int MMA_WARP = 0;   // issues the products of chain 1 (group A and the outputs it feeds); owns TMEM
+constexpr int MMA_WARP2 = 1;  // issues the products of chain 2 (group B and the outputs it feeds)
+constexpr int TMA_WARP = 2;
+constexpr int EW_WARP0 = 3;   // elementwise warps 3..10
+constexpr int NTHREADS = 352;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KB per CTA
 constexpr int SMEM_TAIL = 1024;     // barriers, TMEM base, abort flag, row-sum exchange
@@ -123,7 +128,7 @@ struct Bars {
   uint64_t s_free[2];   // passes 1, 2: stage consumed by the elementwise warps
   uint64_t p_full[2];   // passes 3, 4: [0] = P/ddP written, [1] = dS/dS2 written
   uint64_t out_full;
-  uint64_t teardown;
+  uint64_t teardown[2];
   uint32_t tmem_base;
   int abort_flag;
   float red[BM];
@@ -368,15 +373,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     mbar_init(&bars->stat_full, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bars->strm_full[i], 1);
-      mbar_init(&bars->strm_free[i], 1);
+      mbar_init(&bars->strm_free[i], PASS == 1 ? 1 : 2);  // one commit per issuing chain
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_full[i], PASS == 2 ? 2 : 1);      // pass 2: both chains fill one stage
       mbar_init(&bars->s_free[i], EW_THREADS);
       mbar_init(&bars->p_full[i], EW_THREADS);
     }
-    mbar_init(&bars->out_full, 1);
-    mbar_init(&bars->teardown, 1);
+    mbar_init(&bars->out_full, 2);
+    mbar_init(&bars->teardown[0], 1);
+    mbar_init(&bars->teardown[1], 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -445,11 +451,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         }
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ================================================= MMA issuer
+  } else if (warp == MMA_WARP || warp == MMA_WARP2) {
+    // ================================================= MMA issuers
     // The whole warp runs the loop so that addresses and descriptors stay warp-uniform; one lane
-    // issues the MMAs and commits.
-    if (n_iter > 0) {
+    // issues the MMAs and commits.  chain 0 = group A side, chain 1 = group B side.
+    const int chain = warp == MMA_WARP ? 0 : 1;
+    const bool has_work = n_iter > 0 && (chain == 0 || PASS >= 2);
+    if (has_work) {
       const bool leader = lane == 0;
       auto wait_all = [&](uint64_t* bar, uint32_t parity) {
         return __all_sync(0xffffffffu, wait_bar(bar, parity, bars, p.status)) != 0;
@@ -473,27 +481,26 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       bool ok = wait_all(&bars->stat_full, 0);
       PROF_DECL
 
-      // group A of tile `it`: [S | stat0.strm1^T] as one N = 2*BN product, then A2 += stat1.strm0^T
-      auto issue_group_a = [&](int it, uint32_t acc) -> bool {
+      // score-shaped products of this chain for tile `it` (waits for the tile's shared-memory slot)
+      //   chain 0, group A: [S | stat0.strm1^T] as one N = 2*BN product, then A2 += stat1.strm0^T
+      //   chain 1, group B: [dP | X] (one stacked product in passes 2, 3; two products in pass 4)
+      auto issue_scores = [&](int it, uint32_t acc) -> bool {
         const int slot = it % C::NSLOT;
         PROF_MARK(7)
         if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
         PROF_MARK(0)
         tc_fence_after();
         const uint32_t sl = strm_lo + slot * kSlot16;
-        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
-        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
-        return true;
-      };
-      // group B of tile `it`: [dP | X] (one stacked product in passes 2, 3; two products in pass 4)
-      auto issue_group_b = [&](int it, uint32_t acc) {
-        const uint32_t sl = strm_lo + (it % C::NSLOT) * kSlot16;
-        if (PASS == 4) {
+        if (chain == 0) {
+          gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
+          gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
+        } else if (PASS == 4) {
           gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s1, false);
           gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_lo + 3 * kStat16, k_lo(sl, 2), idesc_s1, false);
         } else {
           gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s2, false);
         }
+        return true;
       };
 
       if (PASS <= 2) {
@@ -503,66 +510,56 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           PROF_MARK(7)
           ok = wait_all(&bars->s_free[stage], ((it / C::NSS) & 1) ^ 1);
           PROF_MARK(1)
-          ok = ok && issue_group_a(it, acc);
+          ok = ok && issue_scores(it, acc);
           if (!ok) break;
-          if (PASS == 2) issue_group_b(it, acc);
           commit(&bars->s_full[stage]);
           commit(&bars->strm_free[it % C::NSLOT]);
           PROF_MARK(2)
         }
       } else {
+        // One TMEM stage, pipelined per chain: scores(t) -> [elementwise half] -> outputs(t) ->
+        // scores(t+1) ...  The bf16 tiles sit where the chain's own accumulators were, and its
+        // MMAs execute in issue order, so scores(t+1) cannot overtake outputs(t).
         const uint32_t acc = tmem_base + C::OUT_COLS;
         const uint32_t out0 = tmem_base, out1 = tmem_base + D;
-        ok = ok && issue_group_a(0, acc);
-        if (ok) {
-          commit(&bars->s_full[0]);
-          issue_group_b(0, acc);
-          commit(&bars->s_full[1]);
-        }
+        ok = ok && issue_scores(0, acc);
+        if (ok) commit(&bars->s_full[chain]);
         PROF_MARK(2)
         for (int it = 0; ok && it < n_iter; ++it) {
           const uint32_t sl = strm_lo + (it % C::NSLOT) * kSlot16;
           const bool accum = it > 0;
-          // outputs fed by group A (P, ddP live where S, A2 were)
           PROF_MARK(7)
-          ok = wait_all(&bars->p_full[0], it & 1);
+          ok = wait_all(&bars->p_full[chain], it & 1);
           if (!ok) break;
           PROF_MARK(3)
           tc_fence_after();
-          gemm_ts<D, BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o, accum);              // ddP . V | dO
-          if (kQStat) gemm_ts<D, BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o, true);   // P . ddV
-          // group A of the next tile may overwrite S/A2 now: the MMAs above were issued first
-          if (it + 1 < n_iter) {
-            ok = issue_group_a(it + 1, acc);
-            if (!ok) break;
-            commit(&bars->s_full[0]);
+          if (chain == 0) {
+            gemm_ts<D, BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o, accum);              // ddP . V | dO
+            if (kQStat) gemm_ts<D, BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o, true);   // P . ddV
+          } else {
+            gemm_ts<D, BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o, accum);  // dS  . ddK | ddQ
+            gemm_ts<D, BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o, true);   // dS2 . K   | Q
           }
-          PROF_MARK(4)
-          // outputs fed by group B (dS, dS2 live where dP, X were)
-          ok = wait_all(&bars->p_full[1], it & 1);
-          if (!ok) break;
-          PROF_MARK(5)
-          tc_fence_after();
-          gemm_ts<D, BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o, accum);  // dS  . ddK | ddQ
-          gemm_ts<D, BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o, true);   // dS2 . K   | Q
           commit(&bars->strm_free[it % C::NSLOT]);
+          PROF_MARK(4)
           if (it + 1 < n_iter) {
-            issue_group_b(it + 1, acc);
-            commit(&bars->s_full[1]);
+            ok = issue_scores(it + 1, acc);
+            if (!ok) break;
+            commit(&bars->s_full[chain]);
           }
           PROF_MARK(6)
         }
       }
 #ifdef FHOB_TC_PROFILE
-      if (leader) PROF_FLUSH(8)
+      if (leader && chain == 0) PROF_FLUSH(8)
 #endif
       if (ok) {
-        commit(&bars->out_full);
+        if (PASS >= 3) commit(&bars->out_full);
       } else {
         // abort path: no tcgen05.mma may still be reading shared memory or TMEM at exit
-        commit(&bars->teardown);
+        commit(&bars->teardown[chain]);
         const long long start = clock64();
-        while (!mbar_try_wait(&bars->teardown, 0)) {
+        while (!mbar_try_wait(&bars->teardown[chain], 0)) {
           if (clock64() - start > kTimeoutCycles) break;
         }
       }
