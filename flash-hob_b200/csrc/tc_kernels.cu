@@ -16,13 +16,16 @@
 //     pass 3: ddO += ddP . V + P . ddV   (after group A)     dQ2 += dS . ddK + dS2 . K     (after group B)
 //     pass 4: dV2 += ddP^T . dO          (after group A)     dK2 += dS^T . ddQ + dS2^T . Q (after group B)
 //
-// Warp roles (352 threads): warps 0 and 1 = MMA issuers (one lane each; warp 0 also allocates
-// TMEM), warp 2 = TMA producer (one lane), warps 3-10 elementwise (warp w owns TMEM lanes
-// 32*(w%4).., column half (w-3)/4).  The products of a tile fall into two chains that never touch
+// Warp roles (384 threads): warps 0, 1 and 3 = MMA issuers (one lane each; warp 0 also allocates
+// TMEM), warp 2 = TMA producer (one lane), warps 4-11 elementwise (warp w owns TMEM lanes
+// 32*(w%4).., column half (w-4)/4).  The products of a tile fall into two chains that never touch
 // the same TMEM columns - chain 1: group A -> P, ddP -> ddO | dV2; chain 2: group B -> dS, dS2 ->
 // dQ2 | dK2 - so each chain has its own issuing warp, on its own warp scheduler.  Issuing a
 // tcgen05.mma keeps a thread busy for about 51 cycles and the elementwise warps of the same
-// scheduler delay it further; one thread cannot feed 64-cycle products under that load, two can.
+// scheduler delay it further; one thread cannot feed 64-cycle products under that load.  For the
+// same reason, in passes 1 and 2 the second product of group A (A2 += stat1 . strm0^T) is issued
+// by a third warp, strictly behind chain 1's stacked product (the tensor pipe runs MMAs in the
+// order they arrive, so the accumulation order stays fixed and results stay bit-reproducible).
 //   passes 1, 2: two score stages in TMEM; the MMA warp runs one tile ahead.
 //   passes 3, 4: TMEM is full with one stage (2*D + 4*64 columns), so the tile is pipelined in
 //   two halves instead: while the elementwise warps turn group A into P / ddP, the tensor core
@@ -48,8 +51,9 @@ constexpr int EW_THREADS = 256;
 constexpr int MMA_WARP = 0;   // issues the products of chain 1 (group A and the outputs it feeds); owns TMEM
 constexpr int MMA_WARP2 = 1;  // issues the products of chain 2 (group B and the outputs it feeds)
 constexpr int TMA_WARP = 2;
-constexpr int EW_WARP0 = 3;   // elementwise warps 3..10
-constexpr int NTHREADS = 352;
+constexpr int MMA_WARP3 = 3;  // issues A2 += stat1 . strm0^T behind chain 1's stacked product
+constexpr int EW_WARP0 = 4;   // elementwise warps 4..11
+constexpr int NTHREADS = 384;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_LIMIT = 232448;  // 227 KB per CTA
 constexpr int SMEM_TAIL = 1024;     // barriers, TMEM base, abort flag, row-sum exchange
@@ -128,7 +132,9 @@ struct Bars {
   uint64_t s_free[2];   // passes 1, 2: stage consumed by the elementwise warps
   uint64_t p_full[2];   // passes 3, 4: [0] = P/ddP written, [1] = dS/dS2 written
   uint64_t out_full;
-  uint64_t teardown[2];
+  uint64_t chain_go;     // passes 3, 4: chain 1 has issued its products of this round (chain 2 may follow)
+  uint64_t teardown[3];
+  uint64_t a2_go;        // chain 1 has issued the stacked product of a tile: the A2 product may follow
   uint32_t tmem_base;
   int abort_flag;
   float red[BM];
@@ -160,11 +166,11 @@ constexpr uint32_t kDescHi = umma_desc_hi_sw128(1024);
 // D (+)= A . B^T with both tiles K-major in shared memory.  a_lo / b_lo are the low descriptor
 // words of the tiles; a K=16 step advances 32 bytes inside a 64-column box, the second box of a
 // D=128 tile starts A_BOX / B_BOX bytes after the first.  The number of B rows (N) is in idesc.
-template <int D, int A_BOX, int B_BOX>
+template <int D, int A_BOX, int B_BOX, int KS0 = 0, int KS1 = D / 16>
 __device__ __forceinline__ void gemm_ss(bool leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
                                         bool accumulate) {
 #pragma unroll
-  for (int ks = 0; ks < D / 16; ++ks) {
+  for (int ks = KS0; ks < KS1; ++ks) {
     const uint32_t a = a_lo + (((ks / 4) * A_BOX + (ks % 4) * 32) >> 4);
     const uint32_t b = b_lo + (((ks / 4) * B_BOX + (ks % 4) * 32) >> 4);
     umma_ss_split(d_tmem, a, b, kDescHi, idesc, (accumulate || ks > 0) ? 1u : 0u, leader);
@@ -338,6 +344,9 @@ template <int PASS, int D, int BN>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
   using C = Cfg<PASS, D, BN>;
   constexpr bool kQStat = PASS != 4;
+  // passes 1, 2: a third warp issues the second product of group A (their tensor pipe has the room;
+  // in passes 3, 4 the extra issuer only delayed group A)
+  constexpr bool kThirdIssuer = PASS <= 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stat_tiles = smem;
   uint8_t* strm_tiles = smem + C::NSTAT * C::STAT_BYTES;
@@ -373,14 +382,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     mbar_init(&bars->stat_full, 1);
     for (int i = 0; i < 4; ++i) {
       mbar_init(&bars->strm_full[i], 1);
-      mbar_init(&bars->strm_free[i], PASS == 1 ? 1 : 2);  // one commit per issuing chain
+      mbar_init(&bars->strm_free[i], PASS == 1 ? 2 : (PASS == 2 ? 3 : 2));  // one commit per issuing warp
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->s_full[i], PASS == 2 ? 2 : 1);      // pass 2: both chains fill one stage
+      // commits per phase: in passes 1, 2 group A comes from two warps; pass 2 adds group B to the stage
+      mbar_init(&bars->s_full[i], PASS == 1 ? 2 : (PASS == 2 ? 3 : 1));
       mbar_init(&bars->s_free[i], EW_THREADS);
       mbar_init(&bars->p_full[i], EW_THREADS);
     }
     mbar_init(&bars->out_full, 2);
+    mbar_init(&bars->chain_go, 1);
+    mbar_init(&bars->a2_go, 1);
+    mbar_init(&bars->teardown[2], 1);
     mbar_init(&bars->teardown[0], 1);
     mbar_init(&bars->teardown[1], 1);
     bars->abort_flag = 0;
@@ -493,7 +506,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         const uint32_t sl = strm_lo + slot * kSlot16;
         if (chain == 0) {
           gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
-          gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
+          if (kThirdIssuer) {
+            // A2 += stat1 . strm0^T is issued by the third warp, strictly behind the stacked product
+            // so that the order of the fp32 accumulation (and with it every result bit) is fixed
+            if (leader) mbar_arrive(&bars->a2_go);
+          } else {
+            gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
+          }
         } else if (PASS == 4) {
           gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s1, false);
           gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_lo + 3 * kStat16, k_lo(sl, 2), idesc_s1, false);
@@ -542,11 +561,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           }
           commit(&bars->strm_free[it % C::NSLOT]);
           PROF_MARK(4)
+          // Chain 1's group A of the next tile gates the next elementwise half, while chain 2's
+          // group B is needed half a tile later: chain 2 lets chain 1 issue first, so the tensor
+          // pipe runs them in that order.
+          if (chain == 1) {
+            ok = wait_all(&bars->chain_go, it & 1);
+            if (!ok) break;
+          }
+          PROF_MARK(5)
           if (it + 1 < n_iter) {
             ok = issue_scores(it + 1, acc);
             if (!ok) break;
             commit(&bars->s_full[chain]);
           }
+          if (chain == 0 && leader) mbar_arrive(&bars->chain_go);
           PROF_MARK(6)
         }
       }
@@ -560,6 +588,42 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         commit(&bars->teardown[chain]);
         const long long start = clock64();
         while (!mbar_try_wait(&bars->teardown[chain], 0)) {
+          if (clock64() - start > kTimeoutCycles) break;
+        }
+      }
+    }
+  } else if (warp == MMA_WARP3) {
+    // ================================================= third issuer: A2 += stat1 . strm0^T
+    if (kThirdIssuer && n_iter > 0) {
+      const bool leader = lane == 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, wait_bar(bar, parity, bars, p.status)) != 0;
+      };
+      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false);
+      constexpr int kStatBox = BM * 128;
+      const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
+      const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
+      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4;
+      bool ok = wait_all(&bars->stat_full, 0);
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const int slot = it % C::NSLOT;
+        const int stage = PASS <= 2 ? it % C::NSS : 0;
+        // chain 1 has waited for the stage and issued [S | stat0.strm1^T], which zero-initialises A2
+        ok = wait_all(&bars->a2_go, it & 1) && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + C::OUT_COLS + (PASS <= 2 ? stage * C::STAGE_COLS : 0);
+        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16,
+                                             strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
+        if (leader) {
+          umma_commit(&bars->s_full[stage]);
+          umma_commit(&bars->strm_free[slot]);
+        }
+      }
+      if (!ok && leader) {
+        umma_commit(&bars->teardown[2]);
+        const long long start = clock64();
+        while (!mbar_try_wait(&bars->teardown[2], 0)) {
           if (clock64() - start > kTimeoutCycles) break;
         }
       }
