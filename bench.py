@@ -52,8 +52,8 @@ GEMM_UNITS = {"pass1": 3, "pass2": 5, "pass3": 9, "pass4": 8}
 # workload's shape (N_Q=4096, N_K=8192, D=128), from the ncu capture summarised in
 # profiles/tc_pass_kernels_cfg5_16heads.md (captured with 16 heads; traffic grows in proportion to
 # the heads, every head having its own tensors).  None for shapes that were not captured.
-DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass1"): 105.48e6 / 16, ("cfg5-shard", "pass2"): 190.34e6 / 16,
-                       ("cfg5-shard", "pass3"): 209.92e6 / 16, ("cfg5-shard", "pass4"): 229.08e6 / 16}
+DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass1"): 104.46e6 / 16, ("cfg5-shard", "pass2"): 192.02e6 / 16,
+                       ("cfg5-shard", "pass3"): 212.66e6 / 16, ("cfg5-shard", "pass4"): 230.63e6 / 16}
 KERNEL_NAMES = {"pass1": "tc_pass_kernel<1, {d}, 128>", "pass2": "tc_pass_kernel<2, {d}, 64>",
                 "pass3": "tc_pass_kernel<3, {d}, 64>", "pass4": "tc_pass_kernel<4, {d}, 64>"}
 
