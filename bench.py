@@ -3,15 +3,16 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl fhob|reference]
 
-One "step" is one call of the operator (pre-pass + four passes) over one batch
+One "step" is one call of the operator (pre-pass + three sweeps) over one batch
 of synthetic heads resident in HBM.  Work is sharded over batch x heads with no
 collective (weak scaling: every GPU gets the same number of heads), so under
 torchrun each rank runs its own shard and the only communication is the
 barrier/max-reduction around the timed region.  Rank 0 prints ONE JSON line.
 
 Flop accounting: F_alg = 24*BH*pairs*D (the 12 distinct contractions of the
-maths) is what `value`, `e2e` and `cpu_baseline` use; F_exec = 50*BH*pairs*D
-(25 contractions issued by the four-pass algorithm) is reported beside it.
+maths) is what `value`, `e2e` and `cpu_baseline` use; F_exec = 44*BH*pairs*D
+(22 contractions issued: 5 by the sweep that yields dd and b, 9 by the dQ2/ddO
+pass, 8 by the dK2/dV2 pass) is reported beside it.
 """
 from __future__ import annotations
 
@@ -47,15 +48,16 @@ WORKLOADS = {
     "n8192": dict(bh=32, n_q=8192, n_k=8192, d=128, causal=False, cot=1.0,
                   desc="bf16 non-causal B=1 H=32 N=8192 D=128"),
 }
-GEMM_UNITS = {"pass1": 3, "pass2": 5, "pass3": 9, "pass4": 8}
+GEMM_UNITS = {"pass12": 5, "pass3": 9, "pass4": 8}
+EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass on the default
 # workload's shape (N_Q=4096, N_K=8192, D=128), from the ncu capture summarised in
 # profiles/tc_pass_kernels_cfg5_16heads.md (captured with 16 heads; traffic grows in proportion to
 # the heads, every head having its own tensors).  None for shapes that were not captured.
-DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass1"): 104.46e6 / 16, ("cfg5-shard", "pass2"): 192.02e6 / 16,
+DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass12"): 192.02e6 / 16,
                        ("cfg5-shard", "pass3"): 212.66e6 / 16, ("cfg5-shard", "pass4"): 230.63e6 / 16}
-KERNEL_NAMES = {"pass1": "tc_pass_kernel<1, {d}, 128>", "pass2": "tc_pass_kernel<2, {d}, 64>",
-                "pass3": "tc_pass_kernel<3, {d}, 64>", "pass4": "tc_pass_kernel<4, {d}, 64>"}
+KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, true>",
+                "pass3": "tc_pass_kernel<3, {d}, 64, false>", "pass4": "tc_pass_kernel<4, {d}, 64, false>"}
 
 
 def pairs(w):
@@ -308,7 +310,7 @@ def main():
 
     # ---- per-pass timing (same stream, CUDA events between the stages)
     lib = _lib.load()
-    stages = ["prepass", "pass1", "pass2", "pass3", "pass4"]
+    stages = ["prepass", "pass12", "pass3", "pass4"]
     acc = {s: 0.0 for s in stages}
     s_ptr = C.c_void_p(prob.stream)
     for it in range(2 + args.steps):
@@ -376,13 +378,13 @@ def main():
         config=dict(workload=args.workload, description=w["desc"], bh_per_gpu=w["bh"], n_q=w["n_q"], n_k=w["n_k"],
                     d=w["d"], causal=w["causal"], parallelism=f"batch*heads sharded over {world} GPU(s), no collective",
                     l2="inputs larger than L2: %.0f MB read per step" % (in_bytes / 1e6)),
-        per_gpu=dict(tflops_alg=value / world, tflops_exec=value / world * 50 / 24,
+        per_gpu=dict(tflops_alg=value / world, tflops_exec=value / world * EXEC_OVER_ALG,
                      frac_bf16_peak_alg=value / world / peaks["burst"],
-                     frac_bf16_peak_exec=value / world * 50 / 24 / peaks["burst"],
-                     frac_bf16_sustained_exec=value / world * 50 / 24 / peaks["sustained"]),
-        flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * 50 / 24),
+                     frac_bf16_peak_exec=value / world * EXEC_OVER_ALG / peaks["burst"],
+                     frac_bf16_sustained_exec=value / world * EXEC_OVER_ALG / peaks["sustained"]),
+        flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * EXEC_OVER_ALG),
         passes=passes, roofline=roofline, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
-        gpu_launches=5 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
+        gpu_launches=4 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

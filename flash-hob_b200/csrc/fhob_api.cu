@@ -159,6 +159,14 @@ int fhob_prepass(const FhobProblem* p, void* stream) {
 
 int fhob_pass1(const FhobProblem* p, void* stream) { return run_pass(1, p, stream); }
 int fhob_pass2(const FhobProblem* p, void* stream) { return run_pass(2, p, stream); }
+int fhob_pass12(const FhobProblem* p, void* stream) {
+  int st = validate(p, false);
+  if (st != FHOB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_tc(*p)) return tc_pass(12, *p, s);
+  st = simt_pass(1, *p, s);
+  return st != FHOB_OK ? st : simt_pass(2, *p, s);
+}
 int fhob_pass3(const FhobProblem* p, void* stream) { return run_pass(3, p, stream); }
 int fhob_pass4(const FhobProblem* p, void* stream) { return run_pass(4, p, stream); }
 
@@ -168,9 +176,17 @@ int fhob_bwdbwd(const FhobProblem* p, void* stream) {
   st = fhob_prepass(p, stream);
   if (st != FHOB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool tc = use_tc(*p);
+  if (use_tc(*p)) {
+    // dd and b come out of one sweep (sum_j P dP = D makes b linear in sums that need no dd)
+    static const int kPasses[3] = {12, 3, 4};
+    for (int pass : kPasses) {
+      st = tc_pass(pass, *p, s);
+      if (st != FHOB_OK) return st;
+    }
+    return FHOB_OK;
+  }
   for (int pass = 1; pass <= 4; ++pass) {
-    st = tc ? tc_pass(pass, *p, s) : simt_pass(pass, *p, s);
+    st = simt_pass(pass, *p, s);
     if (st != FHOB_OK) return st;
   }
   return FHOB_OK;

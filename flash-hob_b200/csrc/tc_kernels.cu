@@ -208,8 +208,11 @@ __device__ __forceinline__ float2 f2(uint32_t lo, uint32_t hi) {
   return make_float2(__uint_as_float(lo), __uint_as_float(hi));
 }
 
-template <int PASS, int BN, bool MASKED>
-__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float2& rowacc) {
+// FUSED (pass 2 only): accumulates r[0] = sum P A2, r[1] = sum P X, r[2] = sum dP P A2, from which
+// both dd and b follow at the end of the pass without dd being known while the tiles stream by.
+template <int PASS, int BN, bool MASKED, bool FUSED>
+__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float2 (&r)[3]) {
+  float2& rowacc = r[0];
   constexpr int CH = BN / 32;
   const float2 sl2 = make_float2(c.sl2, c.sl2), nlc = make_float2(c.r_nlc, c.r_nlc);
   const float2 scale = make_float2(c.scale, c.scale), ndd = make_float2(c.r_ndd, c.r_ndd);
@@ -237,6 +240,11 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
       }
       if (PASS == 1) {
         rowacc = __ffma2_rn(pr, fa2, rowacc);
+      } else if (FUSED) {
+        const float2 q = __fmul2_rn(pr, fa2);
+        r[0] = __fadd2_rn(r[0], q);
+        r[1] = __ffma2_rn(pr, f2(x[j], x[j + 1]), r[1]);
+        r[2] = __ffma2_rn(f2(dp[j], dp[j + 1]), q, r[2]);
       } else {
         const float2 tt = __ffma2_rn(fa2, scale, ndd);
         float2 u = __ffma2_rn(f2(dp[j], dp[j + 1]), tt, f2(x[j], x[j + 1]));
@@ -340,8 +348,9 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
   tmem_st16(acc + 3 * BN, w_ds2);
 }
 
-template <int PASS, int D, int BN>
+template <int PASS, int D, int BN, bool FUSED = false>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
+  static_assert(!FUSED || PASS == 2, "only pass 2 has a fused form");
   using C = Cfg<PASS, D, BN>;
   constexpr bool kQStat = PASS != 4;
   // passes 1, 2: a third warp issues the second product of group A (their tensor pipe has the room;
@@ -643,7 +652,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       c.r_nlc = p.nlc[vec_head + g_row];
       if (PASS >= 2) {
         c.r_k1 = p.k1[vec_head + g_row];
-        c.r_ndd = p.ndd[vec_head + g_row];
+        if (!FUSED) c.r_ndd = p.ndd[vec_head + g_row];
       }
       if (PASS >= 3) c.r_k23 = p.k23[vec_head + g_row];
     }
@@ -657,7 +666,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (c.lo < 0) c.lo = 0;
       c.hi = p.n_q - 1;
     }
-    float2 rowacc = make_float2(0.f, 0.f);
+    float2 racc[3] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    float2& rowacc = racc[0];
     bool ok = true;
     PROF_DECL
 
@@ -678,8 +688,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         PROF_MARK(0)
         tc_fence_after();
         const uint32_t acc = tmem_base + lane_base + stage * C::STAGE_COLS + half * (BN / 2);
-        if (masked) ew_reduce<PASS, BN, true>(acc, col_base, c, rowacc);
-        else ew_reduce<PASS, BN, false>(acc, col_base, c, rowacc);
+        if (masked) ew_reduce<PASS, BN, true, FUSED>(acc, col_base, c, racc);
+        else ew_reduce<PASS, BN, false, FUSED>(acc, col_base, c, racc);
         PROF_MARK(1)
         tc_fence_before();
         mbar_arrive(&bars->s_free[stage]);
@@ -725,7 +735,23 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 #endif
 
     // ---- results
-    if (PASS <= 2) {
+    if (FUSED) {
+      // dd = scale * sum P A2;  b = sum P X + scale * sum dP P A2 - 2 D dd, because sum P dP = D
+      float r1 = racc[0].x + racc[0].y;
+      float rb = (racc[1].x + racc[1].y) + c.scale * (racc[2].x + racc[2].y);
+      if (half == 1) bars->red[row] = r1;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0) r1 += bars->red[row];
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 1) bars->red[row] = rb;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0 && ok && g_row < p.n_q) {
+        rb += bars->red[row];
+        const float dd = c.scale * r1;
+        p.ndd[vec_head + g_row] = -dd;
+        p.k23[vec_head + g_row] = -c.r_k1 * dd - rb;  // -D*dd - b = D*dd - (sum P X + scale * sum dP P A2)
+      }
+    } else if (PASS <= 2) {
       if (half == 1) bars->red[row] = rowacc.x + rowacc.y;
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (half == 0 && ok && g_row < p.n_q) {
@@ -831,9 +857,10 @@ int env_int(const char* name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-template <int PASS, int D, int BN>
+template <int PASS, int D, int BN, bool FUSED = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, D, BN>;
+  constexpr auto kernel = tc_pass_kernel<PASS, D, BN, FUSED>;
   RowVectors rv = row_vectors(p);
   TcParams tp;
   memset(&tp, 0, sizeof(tp));
@@ -855,8 +882,7 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.scale = p.scale;
   const int n_stat = PASS == 4 ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
-  FHOB_CUDA_OK(cudaFuncSetAttribute(tc_pass_kernel<PASS, D, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    C::SMEM_BYTES));
+  FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
   if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
 #ifdef FHOB_TC_PROFILE
@@ -865,7 +891,7 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   FHOB_CUDA_OK(cudaMemsetAsync(prof_dev, 0, 24 * sizeof(unsigned long long), s));
   tp.prof = prof_dev;
 #endif
-  tc_pass_kernel<PASS, D, BN><<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
+  kernel<<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
   FHOB_CUDA_OK(cudaGetLastError());
 #ifdef FHOB_TC_PROFILE
   if (getenv("FHOB_TC_PROF_PRINT")) {
@@ -889,6 +915,7 @@ int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
   switch (pass) {
     case 1: return bn1 == 64 ? launch<1, D, 64>(p, s) : launch<1, D, 128>(p, s);
     case 2: return launch<2, D, 64>(p, s);
+    case 12: return launch<2, D, 64, true>(p, s);  // passes 1 and 2 in one sweep
     case 3: return launch<3, D, 64>(p, s);
     case 4: return launch<4, D, 64>(p, s);
   }

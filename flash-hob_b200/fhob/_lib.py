@@ -16,7 +16,7 @@ ERR_TIMEOUT, ERR_SMEM_ALIGN = 64, 128
 # every symbol include/fhob.h declares
 SYMBOLS = (
     "fhob_version", "fhob_strerror", "fhob_last_cuda_error", "fhob_workspace_bytes", "fhob_bwdbwd",
-    "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
+    "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
     "fhob_read_status", "fhob_forward", "fhob_backward", "fhob_bwdbwd_static_scratch",
 )
 STATIC_SCRATCH_MAX_ROWS = 262144
@@ -53,7 +53,7 @@ def load() -> C.CDLL:
     lib.fhob_last_cuda_error.restype = C.c_char_p
     lib.fhob_workspace_bytes.restype = C.c_size_t
     lib.fhob_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
-    for name in ("fhob_bwdbwd", "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass3", "fhob_pass4",
+    for name in ("fhob_bwdbwd", "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4",
                  "fhob_read_status", "fhob_bwdbwd_static_scratch"):
         fn = getattr(lib, name)
         fn.restype = C.c_int

@@ -217,8 +217,11 @@ def produce_L(Q, K, is_causal: bool = False, scale=None):
     return attention_forward(Q, K, K, scale, is_causal=is_causal)[1]
 
 
-def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl="auto", upto=4):
+def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl="auto", upto=4, fused12=False):
     """Runs the pre-pass and passes 1..``upto`` one by one (unit tests, profiling).
+
+    ``fused12`` replaces passes 1 and 2 by the single sweep that ``flash_bwdbwd``
+    uses on the tensor-core path (``fhob_pass12``).
 
     Returns a dict with the row statistics ``d``, ``dd``, ``b`` (fp32, (BH, N_Q));
     entries a pass has not produced yet are garbage), the outputs produced so
@@ -229,7 +232,12 @@ def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl
     s = C.c_void_p(prob.stream)
     with torch.cuda.device(prob.device):
         _lib.check(lib.fhob_prepass(C.byref(prob.p), s), "fhob_prepass")
-        for i in range(1, upto + 1):
+        stages = [str(i) for i in range(1, upto + 1)]
+        if fused12:
+            if upto < 2:
+                raise ValueError("fused12 needs upto >= 2")
+            stages = ["12"] + stages[2:]
+        for i in stages:
             _lib.check(getattr(lib, f"fhob_pass{i}")(C.byref(prob.p), s), f"fhob_pass{i}")
         vecs = torch.empty(3, prob.bh, prob.n_q, dtype=torch.float32, device=prob.device)
         _lib.check(lib.fhob_row_stats(C.byref(prob.p), C.c_void_p(vecs[0].data_ptr()),

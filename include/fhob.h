@@ -128,6 +128,17 @@ int fhob_pass3(const FhobProblem* p, void* stream);
 int fhob_pass4(const FhobProblem* p, void* stream);
 
 /*
+ * dd and b in one sweep over the keys; equivalent to fhob_pass1 followed by
+ * fhob_pass2 and what fhob_bwdbwd runs on the tensor-core path.  With
+ * sum_j P_ij dP_ij = D_i the reference's b (:236-243) is
+ *   b_i = sum_j P_ij (X_ij + dP_ij ddS_ij) - 2 D_i dd_i,
+ * whose sums do not need dd_i while the tiles stream by, so S, P and ddS
+ * are recomputed once instead of twice (5 contractions instead of 3 + 5).
+ * The reference has no such stage.  (The CUDA-core path runs its two passes.)
+ */
+int fhob_pass12(const FhobProblem* p, void* stream);
+
+/*
  * Copies the row statistics out of the workspace into caller device buffers
  * of bh*n_q floats each, undoing the internal sign/scale folding:
  * d_out = D, dd_out = dd, b_out = b.  Any of the three may be NULL.

@@ -30,7 +30,7 @@ def _oracle(x64, scale, causal):
     return ref, lse, o, stats
 
 
-def _run(x64, scale, causal, dtype, impl, upto=None):
+def _run(x64, scale, causal, dtype, impl, upto=None, fused12=False):
     import fhob
     ref, lse, o, stats = _oracle(x64, scale, causal)
     dev = {k: v.to(dtype).cuda() for k, v in x64.items()}
@@ -40,7 +40,7 @@ def _run(x64, scale, causal, dtype, impl, upto=None):
     if upto is None:
         got = fhob.flash_bwdbwd(*args, is_causal=causal, impl=impl, check=True)
         return got, ref, stats
-    return fhob.run_passes(*args, is_causal=causal, impl=impl, upto=upto), ref, stats
+    return fhob.run_passes(*args, is_causal=causal, impl=impl, upto=upto, fused12=fused12), ref, stats
 
 
 SMALL = [(2, 128, 128, 64), (2, 128, 256, 64), (1, 256, 128, 128), (3, 96, 160, 32), (1, 100, 150, 72)]
@@ -86,6 +86,35 @@ def test_bf16_row_statistics(d, causal, impl, upto):
     assert O.rel_err(res["dd"], sdd) < TOL_BF16
     if upto >= 2:
         assert O.rel_err(res["b"], sb) < TOL_BF16
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [64, 128])
+def test_bf16_row_statistics_single_sweep(d, causal, impl):
+    """dd and b from the one-sweep stage (b = sum P (X + dP ddS) - 2 D dd) against the oracle and
+    against the two reference-shaped passes."""
+    x = make_inputs(2, 256, 384, d, seed=33, dtype=torch.float64)
+    two, _, (sd, sdd, sb) = _run(x, d ** -0.5, causal, torch.bfloat16, impl, upto=2)
+    one, _, _ = _run(x, d ** -0.5, causal, torch.bfloat16, impl, upto=2, fused12=True)
+    assert one["status"] == 0
+    assert O.rel_err(one["dd"], sdd) < TOL_BF16
+    assert O.rel_err(one["b"], sb) < TOL_BF16
+    assert O.rel_err(one["dd"], two["dd"]) < 1e-5
+    assert O.rel_err(one["b"], two["b"]) < 5e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_bf16_offset_cotangents(causal):
+    """Cotangents with a large common component make D and dd large against the fluctuating part of
+    b: the one-sweep form of b subtracts 2 D dd from sums of that size."""
+    x = make_inputs(2, 384, 384, 128, seed=35, dtype=torch.float64)
+    x["do"] = x["do"] + 1.5 * x["v"].mean(dim=1, keepdim=True).sign()
+    x["ddq"] = x["ddq"] + 0.75
+    x["ddk"] = x["ddk"] - 0.5
+    got, ref, _ = _run(x, 128 ** -0.5, causal, torch.bfloat16, "tcgen05")
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
 
 
 BF16_CASES = [(2, 128, 128, 64), (2, 256, 384, 64), (2, 384, 256, 128), (1, 128, 512, 128), (3, 512, 512, 64)]
