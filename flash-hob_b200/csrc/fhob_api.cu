@@ -60,6 +60,7 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
   if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
   if (p->causal != 0 && p->causal != 1) return FHOB_ERR_ARG;
+  if (p->window < 0 || (p->window > 0 && !p->causal) || p->reserved != 0) return FHOB_ERR_ARG;
   const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->lse, p->ddq, p->ddk, p->ddv};
   for (int i = 0; i < (need_cotangents ? 9 : 6); ++i) {
     if (!ins[i]) return FHOB_ERR_ARG;
@@ -101,7 +102,7 @@ using namespace fhob;
 
 extern "C" {
 
-int fhob_version(void) { return 100; }
+int fhob_version(void) { return 200; }
 
 const char* fhob_strerror(int status) {
   switch (status) {
@@ -217,6 +218,7 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
   if (!p || !p->q || !p->k || !p->v || !o_out || !lse_out) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
+  if (p->window < 0 || (p->window > 0 && p->causal != 1)) return FHOB_ERR_ARG;
   return simt_forward(*p, o_out, lse_out, static_cast<cudaStream_t>(stream));
 }
 

@@ -50,6 +50,39 @@ inline RowVectors row_vectors(const FhobProblem& p) {
   return r;
 }
 
+// Mask of the reference (jax_refs/flash_impl.py:86-91): with off = n_k - n_q, key j is visible to
+// query i iff 0 <= i + off - j, and i + off - j < window when a sliding window is set.
+__host__ __device__ inline bool pair_visible(int qi, int kj, int off, int causal, int window) {
+  if (!causal) return true;
+  const int dist = qi + off - kj;
+  return dist >= 0 && (window <= 0 || dist < window);
+}
+
+// Range [t_begin, t_end) of streamed tiles (tn rows each, n_strm rows in all) that can hold a
+// visible pair for the stationary rows [m0, m0 + tm): streamed keys when the queries are
+// stationary, streamed queries when the keys are.
+__host__ __device__ inline void visible_tiles(bool q_stationary, int m0, int tm, int tn, int n_strm, int off,
+                                              int causal, int window, int& t_begin, int& t_end) {
+  t_begin = 0;
+  t_end = (n_strm + tn - 1) / tn;
+  if (!causal) return;
+  long first, last;  // inclusive range of streamed rows visible to any stationary row
+  if (q_stationary) {
+    last = static_cast<long>(m0) + tm - 1 + off;
+    first = window > 0 ? static_cast<long>(m0) + off - window + 1 : 0;
+  } else {
+    first = static_cast<long>(m0) - off;
+    last = window > 0 ? static_cast<long>(m0) + tm - 1 - off + window - 1 : static_cast<long>(n_strm) - 1;
+  }
+  if (last < 0) {
+    t_end = 0;
+  } else if (last / tn + 1 < t_end) {
+    t_end = static_cast<int>(last / tn + 1);
+  }
+  if (first > 0) t_begin = static_cast<int>(first / tn < t_end ? first / tn : t_end);
+  if (t_begin > t_end) t_begin = t_end;
+}
+
 // Per-thread record of the last CUDA error (read through fhob_last_cuda_error).
 void set_cuda_error(cudaError_t e, const char* where);
 void set_cuda_error_text(const char* text);

@@ -27,7 +27,7 @@ struct SimtParams {
   void *dq2, *dk2, *dv2, *ddo;
   const float *nlc, *k1;
   float *ndd, *k23;
-  int n_q, n_k, d, causal;
+  int n_q, n_k, d, causal, window;
   float scale;
 };
 
@@ -133,17 +133,8 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
     for (int m = 0; m < DCH; ++m) out0[i][m] = out1[i][m] = 0.f;
 
   // streamed range
-  int t_begin = 0, t_end = (n_strm + TN - 1) / TN;
-  if (p.causal) {
-    if (kQStationary) {
-      long last_key = static_cast<long>(m0) + TM - 1 + causal_off;  // largest visible key of this tile
-      if (last_key < 0) t_end = 0;
-      else if (last_key / TN + 1 < t_end) t_end = static_cast<int>(last_key / TN + 1);
-    } else {
-      long first_q = static_cast<long>(m0) - causal_off;  // smallest query that sees key m0
-      if (first_q > 0) t_begin = static_cast<int>(first_q / TN);
-    }
-  }
+  int t_begin, t_end;
+  visible_tiles(kQStationary, m0, TM, TN, n_strm, causal_off, p.causal, p.window, t_begin, t_end);
   const float sl2 = p.scale * kLog2e;
 
   for (int t = t_begin; t < t_end; ++t) {
@@ -204,7 +195,7 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
       int r = warp * RPW + i;
       int qi = kQStationary ? m0 + r : n0 + lane;
       int kj = kQStationary ? n0 + lane : m0 + r;
-      bool allowed = qi < p.n_q && kj < p.n_k && (!p.causal || qi + causal_off >= kj);
+      bool allowed = qi < p.n_q && kj < p.n_k && pair_visible(qi, kj, causal_off, p.causal, p.window);
       float nlc, nds, ndd, nbs;
       if (kQStationary) { nlc = r_nlc[i]; nds = r_nds[i]; ndd = r_ndd[i]; nbs = r_nbs[i]; }
       else { nlc = svec[lane]; nds = svec[TN + lane]; ndd = svec[2 * TN + lane]; nbs = svec[3 * TN + lane]; }
@@ -315,14 +306,10 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 #pragma unroll
     for (int m = 0; m < DCH; ++m) acc[i][m] = 0.f;
   }
-  int t_end = (p.n_k + TN - 1) / TN;
-  if (p.causal) {
-    long last_key = static_cast<long>(m0) + TM - 1 + causal_off;
-    if (last_key < 0) t_end = 0;
-    else if (last_key / TN + 1 < t_end) t_end = static_cast<int>(last_key / TN + 1);
-  }
+  int t_begin, t_end;
+  visible_tiles(true, m0, TM, TN, p.n_k, causal_off, p.causal, p.window, t_begin, t_end);
   const float sl2 = p.scale * kLog2e;
-  for (int t = 0; t < t_end; ++t) {
+  for (int t = t_begin; t < t_end; ++t) {
     const int n0 = t * TN;
     __syncthreads();
     load_tile<T>(ks, ld, p.k, koff, n0, TN, p.n_k, d);
@@ -339,7 +326,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
       int r = warp * RPW + i, qi = m0 + r, kj = n0 + lane;
-      bool allowed = qi < p.n_q && kj < p.n_k && (!p.causal || qi + causal_off >= kj);
+      bool allowed = qi < p.n_q && kj < p.n_k && pair_visible(qi, kj, causal_off, p.causal, p.window);
       float sv = allowed ? s[i] * sl2 : -INFINITY;  // log2 domain
       float mnew = fmaxf(mrow[i], warp_max(sv));
       float alpha = (mnew == -INFINITY) ? 1.f : exp2f(mrow[i] - mnew);
@@ -424,17 +411,8 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
   for (int i = 0; i < RPW; ++i)
 #pragma unroll
     for (int m = 0; m < DCH; ++m) acc0[i][m] = acc1[i][m] = 0.f;
-  int t_begin = 0, t_end = (n_strm + TN - 1) / TN;
-  if (p.causal) {
-    if (!KSIDE) {
-      long last_key = static_cast<long>(m0) + TM - 1 + causal_off;
-      if (last_key < 0) t_end = 0;
-      else if (last_key / TN + 1 < t_end) t_end = static_cast<int>(last_key / TN + 1);
-    } else {
-      long first_q = static_cast<long>(m0) - causal_off;
-      if (first_q > 0) t_begin = static_cast<int>(first_q / TN);
-    }
-  }
+  int t_begin, t_end;
+  visible_tiles(!KSIDE, m0, TM, TN, n_strm, causal_off, p.causal, p.window, t_begin, t_end);
   const float sl2 = p.scale * kLog2e;
   for (int t = t_begin; t < t_end; ++t) {
     const int n0 = t * TN;
@@ -468,7 +446,7 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
     for (int i = 0; i < RPW; ++i) {
       const int r = warp * RPW + i;
       const int qi = KSIDE ? n0 + lane : m0 + r, kj = KSIDE ? m0 + r : n0 + lane;
-      const bool allowed = qi < p.n_q && kj < p.n_k && (!p.causal || qi + causal_off >= kj);
+      const bool allowed = qi < p.n_q && kj < p.n_k && pair_visible(qi, kj, causal_off, p.causal, p.window);
       const float nlc = KSIDE ? svec[lane] : r_nlc[i], k1 = KSIDE ? svec[TN + lane] : r_k1[i];
       const float pr = allowed ? exp2f(fmaf(s[i], sl2, nlc)) : 0.f;
       pt[(0 * TM + r) * LT + lane] = pr;
@@ -523,7 +501,7 @@ SimtParams make_params(const FhobProblem& p) {
   s.q = p.q; s.k = p.k; s.v = p.v; s.d_o = p.d_o; s.ddq = p.ddq; s.ddk = p.ddk; s.ddv = p.ddv;
   s.dq2 = p.dq2; s.dk2 = p.dk2; s.dv2 = p.dv2; s.ddo = p.ddo;
   s.nlc = rv.nlc; s.k1 = rv.k1; s.ndd = rv.ndd; s.k23 = rv.k23;
-  s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.causal = p.causal; s.scale = p.scale;
+  s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.causal = p.causal; s.window = p.window; s.scale = p.scale;
   return s;
 }
 

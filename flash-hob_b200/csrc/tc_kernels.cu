@@ -106,7 +106,7 @@ struct TcParams {
   __nv_bfloat16* out0;
   __nv_bfloat16* out1;
   int* status;
-  int n_q, n_k, causal, tiles_per_head;
+  int n_q, n_k, causal, window, tiles_per_head;
   float scale;
 #ifdef FHOB_TC_PROFILE
   unsigned long long* prof;
@@ -371,18 +371,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
   const int n_strm = kQStat ? p.n_k : p.n_q;
   const int off = p.n_k - p.n_q;
 
-  int t_begin = 0, t_end = (n_strm + BN - 1) / BN;
-  if (p.causal) {
-    if (kQStat) {
-      long last_key = static_cast<long>(m0) + BM - 1 + off;
-      if (last_key < 0) t_end = 0;
-      else if (last_key / BN + 1 < t_end) t_end = static_cast<int>(last_key / BN + 1);
-    } else {
-      long first_q = static_cast<long>(m0) - off;
-      if (first_q > 0) t_begin = static_cast<int>(first_q / BN);
-      if (t_begin > t_end) t_begin = t_end;
-    }
-  }
+  int t_begin, t_end;
+  visible_tiles(kQStat, m0, BM, BN, n_strm, off, p.causal, p.window, t_begin, t_end);
   const int n_iter = t_end - t_begin;
 
   // ---- set-up
@@ -661,10 +651,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       c.lo = 0;
       c.hi = p.n_k - 1;
       if (p.causal && g_row + off < c.hi) c.hi = g_row + off;
+      if (p.window > 0 && g_row + off - p.window + 1 > 0) c.lo = g_row + off - p.window + 1;
     } else {
       c.lo = p.causal ? g_row - off : 0;
       if (c.lo < 0) c.lo = 0;
       c.hi = p.n_q - 1;
+      if (p.window > 0 && g_row - off + p.window - 1 < c.hi) c.hi = g_row - off + p.window - 1;
     }
     float2 racc[3] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     float2& rowacc = racc[0];
@@ -678,6 +670,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (p.causal) {
         if (kQStat) masked = masked || (n0 + BN - 1 > m0 + off);
         else masked = masked || (n0 + off < m0 + BM - 1);
+        if (p.window > 0) {
+          // the pair of the tile that is furthest apart: last query row against first key row
+          if (kQStat) masked = masked || (m0 + BM - 1 + off - n0 >= p.window);
+          else masked = masked || (n0 + BN - 1 + off - m0 >= p.window);
+        }
       }
       const int col_base = n0 + half * (BN / 2);
       if constexpr (PASS <= 2) {
@@ -879,7 +876,7 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   tp.out0 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.dq2 : p.dk2);
   tp.out1 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.ddo : p.dv2);
   tp.status = rv.status;
-  tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.scale = p.scale;
+  tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = PASS == 4 ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
   FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));

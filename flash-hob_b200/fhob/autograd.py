@@ -25,14 +25,14 @@ from . import _lib
 from .ops import _fold, _Problem, attention_forward, flash_bwdbwd
 
 
-def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False):
+def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sliding_window=None):
     """First backward from the saved forward results: returns ``(dQ, dK, dV)``.
 
     Same maths as ``attn_bwd`` (jax_refs/flash_impl.py:124-173) with
     ``P = exp(S - L)`` and ``D = rowsum(dO * O)``; O(N) memory.
     """
     # the problem struct wants three cotangent tensors of the right shapes; they are not read
-    prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, "auto", need_outputs=False)
+    prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, "auto", need_outputs=False, window=sliding_window)
     q, k = prob.keep[0], prob.keep[1]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(k)
     with torch.cuda.device(prob.device):
@@ -43,37 +43,38 @@ def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False):
 
 class _AttentionBackward(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, o, lse, d_o, scale, is_causal):
+    def forward(ctx, q, k, v, o, lse, d_o, scale, is_causal, window):
         ctx.save_for_backward(q, k, v, o, lse, d_o)
-        ctx.scale, ctx.is_causal = scale, is_causal
-        return attention_backward(q, k, v, o, d_o, lse, scale, is_causal=is_causal)
+        ctx.scale, ctx.is_causal, ctx.window = scale, is_causal, window
+        return attention_backward(q, k, v, o, d_o, lse, scale, is_causal=is_causal, sliding_window=window)
 
     @staticmethod
     def backward(ctx, ddq, ddk, ddv):
         q, k, v, o, lse, d_o = ctx.saved_tensors
         dq2, dk2, dv2, ddo = flash_bwdbwd(q, k, v, o, d_o, ddq.contiguous(), ddk.contiguous(), ddv.contiguous(), lse,
-                                          ctx.scale, is_causal=ctx.is_causal)
-        return dq2, dk2, dv2, None, None, ddo, None, None
+                                          ctx.scale, is_causal=ctx.is_causal, sliding_window=ctx.window)
+        return dq2, dk2, dv2, None, None, ddo, None, None, None
 
 
 class _Attention(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, is_causal):
-        o, lse = attention_forward(q, k, v, scale, is_causal=is_causal)
+    def forward(ctx, q, k, v, scale, is_causal, window):
+        o, lse = attention_forward(q, k, v, scale, is_causal=is_causal, sliding_window=window)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.scale, ctx.is_causal = scale, is_causal
+        ctx.scale, ctx.is_causal, ctx.window = scale, is_causal, window
         return o
 
     @staticmethod
     def backward(ctx, d_o):
         q, k, v, o, lse = ctx.saved_tensors
-        dq, dk, dv = _AttentionBackward.apply(q, k, v, o, lse, d_o.contiguous(), ctx.scale, ctx.is_causal)
-        return dq, dk, dv, None, None
+        dq, dk, dv = _AttentionBackward.apply(q, k, v, o, lse, d_o.contiguous(), ctx.scale, ctx.is_causal,
+                                              ctx.window)
+        return dq, dk, dv, None, None, None
 
 
-def attention(q, k, v, scale=None, *, is_causal: bool = False):
+def attention(q, k, v, scale=None, *, is_causal: bool = False, sliding_window=None):
     """``softmax(q k^T scale) v`` for CUDA bfloat16/float32 tensors ``(BH, N, D)`` or ``(B, H, N, D)``,
     differentiable twice (``create_graph=True``)."""
     if scale is None:
         scale = q.shape[-1] ** -0.5
-    return _Attention.apply(q, k, v, float(scale), bool(is_causal))
+    return _Attention.apply(q, k, v, float(scale), bool(is_causal), sliding_window)

@@ -35,10 +35,23 @@ def _fold(t: torch.Tensor, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
+def _window(is_causal, sliding_window) -> int:
+    """0 for no window, else the validated sliding_window_length."""
+    if sliding_window is None or sliding_window == float("inf"):
+        return 0
+    w = int(sliding_window)
+    if w != sliding_window or w < 1 or w > 2 ** 31 - 1:
+        raise ValueError(f"sliding_window must be a positive integer, got {sliding_window!r}")
+    if not is_causal:
+        raise ValueError("sliding_window needs is_causal=True (the window trails the causal diagonal)")
+    return w
+
+
 class _Problem:
     """Validated tensors + the FhobProblem struct that points at them."""
 
-    def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True):
+    def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True,
+                 window=None):
         names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
         tensors = [Q, K, V, O, dO, ddQ, ddK, ddV]
         if impl not in _lib.IMPL:
@@ -79,6 +92,7 @@ class _Problem:
         p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
         p.dtype = _lib.FHOB_BF16 if dt == torch.bfloat16 else _lib.FHOB_F32
         p.causal = 1 if is_causal else 0
+        p.window = _window(is_causal, window)
         p.impl = _lib.IMPL[impl]
         p.scale = float(scale)
         p.q, p.k, p.v, p.o, p.d_o = (t.data_ptr() for t in (q, k, v, o, do))
@@ -100,8 +114,8 @@ class _Problem:
         return _lib.load().fhob_read_status(C.byref(self.p), C.c_void_p(self.stream))
 
 
-def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check):
-    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl)
+def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, window=None):
+    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, window=window)
     lib = _lib.load()
     with torch.cuda.device(prob.device):
         _lib.check(lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream)), "fhob_bwdbwd")
@@ -111,7 +125,7 @@ def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check)
 
 
 def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = False,
-                 impl: str = "auto", check: bool = False,
+                 sliding_window: Optional[int] = None, impl: str = "auto", check: bool = False,
                  device: Optional[torch.device] = None) -> Tuple[torch.Tensor, ...]:
     """Double backward of scaled-dot-product attention.
 
@@ -123,7 +137,9 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
 
     Keyword-only additions, all behaviour-preserving by default:
     ``is_causal`` bottom-right aligned causal mask (the reference operator has
-    none; its oracle does: jax_refs/flash_impl.py:86-91); ``impl`` one of
+    none; its oracle does: jax_refs/flash_impl.py:86-91); ``sliding_window``
+    the oracle's ``sliding_window_length`` W (needs ``is_causal``): query i
+    then sees only the W keys that end at its causal diagonal; ``impl`` one of
     "auto", "simt", "tcgen05"; ``check`` synchronise and raise if a device
     wait timed out.
 
@@ -133,17 +149,17 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     a stream synchronise.
     """
     if Q.device.type == "cuda":
-        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check)
+        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, sliding_window)
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev)
+    return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev, window=sliding_window)
 
 
 _copy_streams: dict = {}
 
 
-def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8):
+def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8, window=None):
     """Host tensors in, pinned host tensors out.  Heads are independent, so the batch is cut into
     up to `max_chunks` head ranges that flow through three streams: upload of range i+1, the
     kernels of range i and the download of range i-1 overlap."""
@@ -168,7 +184,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8):
         main.wait_event(ready)
         for t in staged:
             t.record_stream(main)
-        res = _run_device(*staged, scale, is_causal, impl, check)  # check=True synchronises per range
+        res = _run_device(*staged, scale, is_causal, impl, check, window)  # check=True synchronises per range
         done = torch.cuda.Event()
         done.record(main)
         down.wait_event(done)
@@ -181,7 +197,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8):
             outs_host[3].reshape(shape_q))
 
 
-def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False):
+def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None):
     """O(N)-memory producer of the saved forward results: returns ``(O, L)``.
 
     ``O = softmax(Q K^T scale) V`` in the input dtype and the fp32 logsumexp
@@ -202,6 +218,7 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False):
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
     p.dtype = _lib.FHOB_BF16 if q.dtype == torch.bfloat16 else _lib.FHOB_F32
     p.causal, p.impl, p.scale = (1 if is_causal else 0), 0, float(scale)
+    p.window = _window(is_causal, sliding_window)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
@@ -210,14 +227,15 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False):
     return o.reshape(shape_q), lse.reshape(shape_q[:-1])
 
 
-def produce_L(Q, K, is_causal: bool = False, scale=None):
+def produce_L(Q, K, is_causal: bool = False, scale=None, sliding_window: Optional[int] = None):
     """fp32 logsumexp of the scaled scores, same name and argument order as the
     reference helper (fhog/triton_flash.py:252-258) but O(N) memory, fp32 and
     causal-capable."""
-    return attention_forward(Q, K, K, scale, is_causal=is_causal)[1]
+    return attention_forward(Q, K, K, scale, is_causal=is_causal, sliding_window=sliding_window)[1]
 
 
-def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl="auto", upto=4, fused12=False):
+def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, sliding_window=None, impl="auto",
+               upto=4, fused12=False):
     """Runs the pre-pass and passes 1..``upto`` one by one (unit tests, profiling).
 
     ``fused12`` replaces passes 1 and 2 by the single sweep that ``flash_bwdbwd``
@@ -227,7 +245,7 @@ def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, impl
     entries a pass has not produced yet are garbage), the outputs produced so
     far, and the device ``status`` word.
     """
-    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl)
+    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, window=sliding_window)
     lib = _lib.load()
     s = C.c_void_p(prob.stream)
     with torch.cuda.device(prob.device):

@@ -65,6 +65,9 @@ typedef struct FhobProblem {
   int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j */
   int32_t impl;    /* FHOB_IMPL_* */
   float scale;     /* softmax scale */
+  int32_t window;  /* sliding_window_length of jax_refs/flash_impl.py:86-91: 0 = none; W > 0 (needs causal = 1)
+                      additionally hides keys with (i + n_k - n_q) - j >= W */
+  int32_t reserved; /* must be 0 */
   /* inputs, device pointers */
   const void* q;   /* (bh, n_q, d) */
   const void* k;   /* (bh, n_k, d) */

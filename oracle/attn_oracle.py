@@ -69,20 +69,20 @@ def _scores(q, k, scale, is_causal, sliding_window_length=math.inf):
     return s
 
 
-def attn_fwd(q, k, v, scale, is_causal=False):
+def attn_fwd(q, k, v, scale, is_causal=False, sliding_window_length=math.inf):
     """O = softmax(QK^T scale) V   (jax_refs/flash_impl.py:94-121)."""
-    p = torch.softmax(_scores(q, k, scale, is_causal), dim=-1)
+    p = torch.softmax(_scores(q, k, scale, is_causal, sliding_window_length), dim=-1)
     return p @ v
 
 
-def attn_lse(q, k, scale, is_causal=False):
+def attn_lse(q, k, scale, is_causal=False, sliding_window_length=math.inf):
     """Row-wise logsumexp of the (masked) scores; the ``stats``/``L`` input."""
-    return torch.logsumexp(_scores(q, k, scale, is_causal), dim=-1)
+    return torch.logsumexp(_scores(q, k, scale, is_causal, sliding_window_length), dim=-1)
 
 
-def attn_bwd(q, k, v, do, scale, is_causal=False):
+def attn_bwd(q, k, v, do, scale, is_causal=False, sliding_window_length=math.inf):
     """First backward (dq, dk, dv), jax_refs/flash_impl.py:124-173."""
-    p = torch.softmax(_scores(q, k, scale, is_causal), dim=-1)
+    p = torch.softmax(_scores(q, k, scale, is_causal, sliding_window_length), dim=-1)
     dp = do @ v.transpose(-1, -2)
     pdp = p * dp
     d = pdp.sum(dim=-1, keepdim=True)
@@ -93,7 +93,7 @@ def attn_bwd(q, k, v, do, scale, is_causal=False):
     return dq, dk, dv
 
 
-def bwdbwd_autograd(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False):
+def bwdbwd_autograd(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, sliding_window_length=math.inf):
     """Form A: vector-Jacobian product of ``attn_bwd`` by reverse-mode autograd.
 
     Same idiom as ``jax.vjp(attn_bwd, q, k, v, do)`` applied to the cotangents
@@ -101,20 +101,21 @@ def bwdbwd_autograd(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False):
     fhog/jax_refs/jax_impl.py:522-532).  Returns (dq2, dk2, dv2, ddo).
     """
     q, k, v, do = (t.detach().clone().requires_grad_(True) for t in (q, k, v, do))
-    dq, dk, dv = attn_bwd(q, k, v, do, scale, is_causal)
+    dq, dk, dv = attn_bwd(q, k, v, do, scale, is_causal, sliding_window_length)
     dq2, dk2, dv2, ddo = torch.autograd.grad(
         (dq, dk, dv), (q, k, v, do), grad_outputs=(ddq, ddk, ddv))
     return dq2, dk2, dv2, ddo
 
 
-def bwdbwd_closed_form(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, lse=None, o=None):
+def bwdbwd_closed_form(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, lse=None, o=None,
+                       sliding_window_length=math.inf):
     """Form B: the closed-form equations of jax_refs/flash_impl.py:176-229.
 
     When ``lse`` (and ``o``) are given the LSE-based variant of
     jax_refs/flash_impl.py:262-328 is evaluated instead: P = exp(S - lse) and
     D = rowsum(o * do).  Masked pairs contribute exactly zero.
     """
-    s = _scores(q, k, scale, is_causal)
+    s = _scores(q, k, scale, is_causal, sliding_window_length)
     if lse is None:
         p = torch.softmax(s, dim=-1)
     else:
@@ -139,11 +140,11 @@ def bwdbwd_closed_form(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, lse=N
     return dq2, dk2, dv2, ddo
 
 
-def bwdbwd_row_stats(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False):
+def bwdbwd_row_stats(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, sliding_window_length=math.inf):
     """The three per-query row statistics the four-pass algorithm stages:
     ``d = rowsum(P*dP)``, ``dd = rowsum(ddS*P)``, ``b = rowsum(dP2*P)``
     (jax_refs/flash_impl.py:232-259, ``precompute_values``)."""
-    s = _scores(q, k, scale, is_causal)
+    s = _scores(q, k, scale, is_causal, sliding_window_length)
     p = torch.softmax(s, dim=-1)
     dp = do @ v.transpose(-1, -2)
     dds = scale * (ddq @ k.transpose(-1, -2) + q @ ddk.transpose(-1, -2))
@@ -160,7 +161,8 @@ def rel_err(x: torch.Tensor, ref: torch.Tensor) -> float:
     return float((x.double().cpu() - ref.cpu()).abs().max() / ref.abs().max().clamp_min(1e-300))
 
 
-def bwdbwd_closed_form_chunked(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, chunk=1024):
+def bwdbwd_closed_form_chunked(q, k, v, do, ddq, ddk, ddv, scale, is_causal=False, chunk=1024,
+                               sliding_window_length=math.inf):
     """Form B evaluated over query-row chunks so that no (N_Q, N_K) matrix is
     ever held whole: memory is O(chunk * N_K).  Same equations as
     ``bwdbwd_closed_form``; works on any device/dtype torch supports (the
@@ -183,7 +185,10 @@ def bwdbwd_closed_form_chunked(q, k, v, do, ddq, ddk, ddv, scale, is_causal=Fals
         s = (qc @ k.T) * scale
         if is_causal:
             qi = torch.arange(r0, r1, device=q.device)[:, None] + off
-            s = torch.where(qi >= kj, s, torch.full_like(s, -math.inf))
+            vis = qi >= kj
+            if sliding_window_length != math.inf:
+                vis = vis & ((qi - kj) < sliding_window_length)
+            s = torch.where(vis, s, torch.full_like(s, -math.inf))
         l = torch.logsumexp(s, dim=-1)
         p = torch.exp(s - l[:, None])
         lse[r0:r1] = l

@@ -333,3 +333,88 @@ def test_autograd_grad_of_grad(causal):
         got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
         for n, g, r in zip(OUT_NAMES, got, ref):
             assert O.rel_err(g, r) < tol, (n, dtype)
+
+
+# ---- sliding window (sliding_window_length of jax_refs/flash_impl.py:86-91)
+
+WINDOW_CASES = [
+    # bh, nq, nk, d, window
+    (2, 256, 256, 64, 17),     # narrower than a tile
+    (2, 384, 384, 128, 64),    # exactly one streamed tile
+    (1, 512, 512, 128, 200),   # spans several tiles, not a multiple of any tile size
+    (2, 256, 448, 64, 100),    # more keys than queries: leading keys are visible to no query
+    (1, 200, 328, 128, 77),    # ragged lengths
+    (1, 256, 256, 64, 4096),   # window wider than the sequence = plain causal
+]
+
+
+def _window_case(bh, nq, nk, d, w, dtype, impl):
+    import fhob
+    x = make_inputs(bh, nq, nk, d, seed=101, dtype=torch.float64)
+    scale = d ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, True, sliding_window_length=w)
+    o = O.attn_fwd(x["q"], x["k"], x["v"], scale, True, sliding_window_length=w)
+    lse = O.attn_lse(x["q"], x["k"], scale, True, sliding_window_length=w)
+    dev = {k: v.to(dtype).cuda() for k, v in x.items()}
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o.to(dtype).cuda(), dev["do"], dev["ddq"], dev["ddk"],
+                            dev["ddv"], lse.float().cuda(), scale, is_causal=True, sliding_window=w, impl=impl,
+                            check=True)
+    return got, ref
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("bh,nq,nk,d,w", WINDOW_CASES)
+def test_bf16_sliding_window(bh, nq, nk, d, w, impl):
+    got, ref = _window_case(bh, nq, nk, d, w, torch.bfloat16, impl)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
+
+
+@pytest.mark.parametrize("bh,nq,nk,d,w", WINDOW_CASES[:4])
+def test_fp32_sliding_window(bh, nq, nk, d, w):
+    got, ref = _window_case(bh, nq, nk, d, w, torch.float32, "auto")
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_F32, n
+
+
+def test_sliding_window_keys_outside_every_window_get_zero():
+    """With more keys than queries the first keys lie before every query's window."""
+    got, _ = _window_case(1, 128, 512, 64, 32, torch.bfloat16, "tcgen05")
+    n_dead = 512 - 128 - 32 + 1   # keys j with (0 + n_k - n_q) - j >= window
+    assert torch.count_nonzero(got[1][:, :n_dead]) == 0 and torch.count_nonzero(got[2][:, :n_dead]) == 0
+    assert torch.count_nonzero(got[1][:, n_dead]) > 0
+
+
+def test_sliding_window_forward_backward_and_autograd():
+    """Forward producer, first backward and the twice-differentiable function with a window."""
+    import fhob
+    w, scale = 50, 0.125
+    x = make_inputs(2, 192, 256, 64, seed=103, dtype=torch.float64)
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, True, sliding_window_length=w)
+    lse_ref = O.attn_lse(x["q"], x["k"], scale, True, sliding_window_length=w)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, True, sliding_window_length=w)
+    ref = O.bwdbwd_autograd(*x.values(), scale, True, sliding_window_length=w)
+    q, k, v, do = (x[n].float().cuda().requires_grad_(True) for n in ("q", "k", "v", "do"))
+    o, lse = fhob.attention_forward(q.detach(), k.detach(), v.detach(), scale, is_causal=True, sliding_window=w)
+    assert O.rel_err(o, o_ref) < TOL_F32 and O.rel_err(lse, lse_ref) < TOL_F32
+    out = fhob.attention(q, k, v, scale, is_causal=True, sliding_window=w)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), do, create_graph=True)
+    for n, g, r in zip(("dq", "dk", "dv"), (dq, dk, dv), first_ref):
+        assert O.rel_err(g.detach(), r) < TOL_F32, n
+    cot = tuple(x[n].float().cuda() for n in ("ddq", "ddk", "ddv"))
+    got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < 2e-4, n
+
+
+def test_sliding_window_argument_errors():
+    import fhob
+    x = {k: v.bfloat16().cuda() for k, v in make_inputs(1, 128, 128, 64, seed=105, dtype=torch.float32).items()}
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 0.125)
+    args = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 0.125)
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, sliding_window=16)              # needs is_causal
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, is_causal=True, sliding_window=0)
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, is_causal=True, sliding_window=2.5)

@@ -96,3 +96,30 @@ def test_row_stats_linear_in_cotangents():
     assert O.rel_err(scaled[0], base[0]) < 1e-13
     assert O.rel_err(scaled[1], 2.5 * base[1]) < 1e-13
     assert O.rel_err(scaled[2], 2.5 * base[2]) < 1e-12
+
+
+def test_sliding_window_mask_definition():
+    """jax_refs/flash_impl.py:86-91: visible iff 0 <= (i + nk - nq) - j < sliding_window_length."""
+    for nq, nk, w in [(5, 9, 3), (8, 8, 1), (7, 4, 2), (6, 10, 100)]:
+        m = O.bottom_right_mask(nq, nk, w)
+        for i in range(nq):
+            for j in range(nk):
+                dist = i + nk - nq - j
+                assert bool(m[i, j]) == (0 <= dist < w)
+
+
+@pytest.mark.parametrize("nq,nk,w", [(48, 48, 7), (40, 72, 16), (64, 64, 64)])
+def test_sliding_window_autograd_equals_closed_form(nq, nk, w):
+    x = make_inputs(2, nq, nk, 16, seed=5, dtype=torch.float64)
+    a = O.bwdbwd_autograd(*x.values(), 0.25, True, sliding_window_length=w)
+    b = O.bwdbwd_closed_form(*x.values(), 0.25, True, sliding_window_length=w)
+    for u, v in zip(a, b):
+        assert O.rel_err(u, v) < 1e-12
+    if w >= nk:  # a window that covers every key is the plain causal mask
+        c = O.bwdbwd_closed_form(*x.values(), 0.25, True)
+        for u, v in zip(b, c):
+            assert torch.equal(u, v)
+    # the query-chunked form used at large sizes agrees too
+    ch = O.bwdbwd_closed_form_chunked(*(t[0] for t in x.values()), 0.25, True, chunk=16, sliding_window_length=w)
+    for u, v in zip(ch[:4], b):
+        assert O.rel_err(u, v[0]) < 1e-12
