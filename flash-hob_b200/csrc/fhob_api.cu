@@ -57,7 +57,7 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = true) {
   if (!p) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0) return FHOB_ERR_ARG;
-  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
+  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
   if (p->causal != 0 && p->causal != 1) return FHOB_ERR_ARG;
   if (p->window < 0 || (p->window > 0 && !p->causal) || p->reserved != 0) return FHOB_ERR_ARG;
@@ -73,7 +73,7 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
       if (!aligned16(x)) return FHOB_ERR_ALIGN;
     }
   }
-  size_t row_bytes = static_cast<size_t>(p->d) * (p->dtype == FHOB_BF16 ? 2 : 4);
+  size_t row_bytes = static_cast<size_t>(p->d) * (p->dtype == FHOB_F32 ? 4 : 2);
   if (row_bytes % 16 != 0) return FHOB_ERR_SHAPE;  // rows must stay 16-byte aligned
   if (p->d > 128) return FHOB_ERR_SHAPE;
   if (!p->workspace || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) return FHOB_ERR_WORKSPACE;
@@ -143,6 +143,10 @@ static int run_prepass(const FhobProblem* p, void* stream) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
         rv.status, rows, p->d, p->scale);
+  } else if (p->dtype == FHOB_F16) {
+    prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
+                                                       static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
+                                                       rv.status, rows, p->d, p->scale);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
@@ -217,7 +221,7 @@ int fhob_read_status(const FhobProblem* p, void* stream) {
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream) {
   if (!p || !p->q || !p->k || !p->v || !o_out || !lse_out) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
-  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32) return FHOB_ERR_ARG;
+  if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->window < 0 || (p->window > 0 && p->causal != 1)) return FHOB_ERR_ARG;
   return simt_forward(*p, o_out, lse_out, static_cast<cudaStream_t>(stream));
 }

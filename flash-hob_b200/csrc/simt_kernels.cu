@@ -41,8 +41,16 @@ template <>
 __device__ __forceinline__ float ld_elem<__nv_bfloat16>(const void* p, size_t i) {
   return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
 }
+template <>
+__device__ __forceinline__ float ld_elem<__half>(const void* p, size_t i) {
+  return __half2float(static_cast<const __half*>(p)[i]);
+}
 template <typename T>
 __device__ __forceinline__ void st_elem(void* p, size_t i, float v);
+template <>
+__device__ __forceinline__ void st_elem<__half>(void* p, size_t i, float v) {
+  static_cast<__half*>(p)[i] = __float2half_rn(v);
+}
 template <>
 __device__ __forceinline__ void st_elem<float>(void* p, size_t i, float v) {
   static_cast<float*>(p)[i] = v;
@@ -547,13 +555,16 @@ int launch_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStre
 
 int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t st) {
   if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
-  return p.dtype == FHOB_F32 ? launch_backward<float>(p, dq, dk, dv, st)
-                             : launch_backward<__nv_bfloat16>(p, dq, dk, dv, st);
+  if (p.dtype == FHOB_F32) return launch_backward<float>(p, dq, dk, dv, st);
+  if (p.dtype == FHOB_F16) return launch_backward<__half>(p, dq, dk, dv, st);
+  return launch_backward<__nv_bfloat16>(p, dq, dk, dv, st);
 }
 
 int simt_pass(int pass, const FhobProblem& p, cudaStream_t st) {
   if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
-  return p.dtype == FHOB_F32 ? dispatch_pass<float>(pass, p, st) : dispatch_pass<__nv_bfloat16>(pass, p, st);
+  if (p.dtype == FHOB_F32) return dispatch_pass<float>(pass, p, st);
+  if (p.dtype == FHOB_F16) return dispatch_pass<__half>(pass, p, st);
+  return dispatch_pass<__nv_bfloat16>(pass, p, st);
 }
 
 int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t st) {
@@ -565,6 +576,10 @@ int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t
     FHOB_CUDA_OK(cudaFuncSetAttribute(simt_forward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
     simt_forward_kernel<float><<<grid, NT, smem, st>>>(s, o_out, lse_out);
+  } else if (p.dtype == FHOB_F16) {
+    FHOB_CUDA_OK(cudaFuncSetAttribute(simt_forward_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+    simt_forward_kernel<__half><<<grid, NT, smem, st>>>(s, o_out, lse_out);
   } else {
     FHOB_CUDA_OK(cudaFuncSetAttribute(simt_forward_kernel<__nv_bfloat16>,
                                       cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));

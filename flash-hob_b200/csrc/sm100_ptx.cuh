@@ -135,11 +135,12 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   return d;
 }
 
-// Instruction descriptor, kind::f16: bf16 x bf16 -> fp32, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
+// Instruction descriptor, kind::f16: bf16 x bf16 (or f16 x f16) -> fp32, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major,
+                                                       bool f16 = false) {
   return (1u << 4)                                   // D format: f32
-         | (1u << 7)                                 // A format: bf16
-         | (1u << 10)                                // B format: bf16
+         | ((f16 ? 0u : 1u) << 7)                    // A format: 0 = f16, 1 = bf16
+         | ((f16 ? 0u : 1u) << 10)                   // B format
          | (static_cast<uint32_t>(a_mn_major) << 15)
          | (static_cast<uint32_t>(b_mn_major) << 16)
          | (static_cast<uint32_t>(n >> 3) << 17)
@@ -215,6 +216,16 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Same for IEEE half precision.
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  return F16 ? pack_f16(lo, hi) : pack_bf16(lo, hi);
 }
 
 }  // namespace ptx

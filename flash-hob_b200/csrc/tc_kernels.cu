@@ -103,8 +103,8 @@ struct TcParams {
   const float* k1;   // -D
   float* ndd;        // -dd           (written by pass 1)
   float* k23;        // -D*dd - b     (written by pass 2)
-  __nv_bfloat16* out0;
-  __nv_bfloat16* out1;
+  uint16_t* out0;  // 16-bit elements: bf16 or f16
+  uint16_t* out1;
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
   float scale;
@@ -259,7 +259,7 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
 // per packed fp32 instruction (fma/mul/add .f32x2).
 // First half of a tile: S, A2 -> P = exp2(S*sl2 + nlc), t = scale*A2 - dd; writes ddP = P t (and P
 // in pass 3) as bf16 over the accumulators and keeps P and t in registers for the second half.
-template <int PASS, bool MASKED>
+template <int PASS, bool MASKED, bool F16>
 __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           float2 (&ps)[16], float2 (&tt)[16]) {
   constexpr bool kQStat = PASS != 4;
@@ -295,8 +295,8 @@ __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in
       const float2 ddp = __fmul2_rn(pr, t);
       ps[j / 2] = pr;
       tt[j / 2] = t;
-      w_ddp[j / 2] = pack_bf16(ddp.x, ddp.y);
-      if (PASS == 3) w_p[j / 2] = pack_bf16(pr.x, pr.y);
+      w_ddp[j / 2] = pack16<F16>(ddp.x, ddp.y);
+      if (PASS == 3) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
     }
   }
   // the bf16 tiles overwrite accumulator columns this thread has already consumed
@@ -306,7 +306,7 @@ __device__ __forceinline__ void ew_half_a(uint32_t acc, int col_base, int col_in
 
 // Second half: dP' = dP - D, X' = X - D*dd - b; writes P dP' and P (dP' t + X'), i.e. dS/scale and
 // dS2/scale: the factor `scale` is applied once to the finished dQ2 / dK2 accumulator instead.
-template <int PASS, bool MASKED>
+template <int PASS, bool MASKED, bool F16>
 __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           const float2 (&ps)[16], const float2 (&tt)[16]) {
   constexpr bool kQStat = PASS != 4;
@@ -340,15 +340,15 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
         ds.x = ok0 ? ds.x : 0.f;   ds.y = ok1 ? ds.y : 0.f;
         ds2.x = ok0 ? ds2.x : 0.f; ds2.y = ok1 ? ds2.y : 0.f;
       }
-      w_ds[j / 2] = pack_bf16(ds.x, ds.y);
-      w_ds2[j / 2] = pack_bf16(ds2.x, ds2.y);
+      w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
+      w_ds2[j / 2] = pack16<F16>(ds2.x, ds2.y);
     }
   }
   tmem_st16(acc + 2 * BN, w_ds);
   tmem_st16(acc + 3 * BN, w_ds2);
 }
 
-template <int PASS, int D, int BN, bool FUSED = false>
+template <int PASS, int D, int BN, bool FUSED = false, bool F16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
   static_assert(!FUSED || PASS == 2, "only pass 2 has a fused form");
   using C = Cfg<PASS, D, BN>;
@@ -477,9 +477,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       auto commit = [&](uint64_t* bar) {
         if (leader) umma_commit(bar);
       };
-      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false);      // one streamed tile
-      constexpr uint32_t idesc_s2 = umma_idesc_bf16(BM, 2 * BN, false, false);  // a stacked pair
-      constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true);
+      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false, F16);      // one streamed tile
+      constexpr uint32_t idesc_s2 = umma_idesc_bf16(BM, 2 * BN, false, false, F16);  // a stacked pair
+      constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true, F16);
       constexpr int kStatBox = BM * 128;
       // low descriptor words of the tiles: K-major use (LBO field unused, set to 1) and MN-major
       // use of streamed tile i (LBO = distance between its two 64-column boxes)
@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       auto wait_all = [&](uint64_t* bar, uint32_t parity) {
         return __all_sync(0xffffffffu, wait_bar(bar, parity, bars, p.status)) != 0;
       };
-      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false);
+      constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false, F16);
       constexpr int kStatBox = BM * 128;
       const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
       const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
@@ -706,8 +706,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         if (!ok) break;
         PROF_MARK(0)
         tc_fence_after();
-        if (masked) ew_half_a<PASS, true>(acc, col_base, half * (BN / 2), c, ps, tt);
-        else ew_half_a<PASS, false>(acc, col_base, half * (BN / 2), c, ps, tt);
+        if (masked) ew_half_a<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
+        else ew_half_a<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[0]);
@@ -716,8 +716,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         if (!ok) break;
         PROF_MARK(4)
         tc_fence_after();
-        if (masked) ew_half_b<PASS, true>(acc, col_base, half * (BN / 2), c, ps, tt);
-        else ew_half_b<PASS, false>(acc, col_base, half * (BN / 2), c, ps, tt);
+        if (masked) ew_half_b<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
+        else ew_half_b<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[1]);
@@ -762,7 +762,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (ok) {
 #pragma unroll
         for (int o = 0; o < 2; ++o) {
-          __nv_bfloat16* dst = (o == 0 ? p.out0 : p.out1) +
+          uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
                                (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
 #pragma unroll
           for (int ch = 0; ch < D / 32; ++ch) {
@@ -780,14 +780,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             }
             if (g_row < n_stat) {
               uint4 w0, w1;
-              w0.x = pack_bf16(__uint_as_float(v[0]), __uint_as_float(v[1]));
-              w0.y = pack_bf16(__uint_as_float(v[2]), __uint_as_float(v[3]));
-              w0.z = pack_bf16(__uint_as_float(v[4]), __uint_as_float(v[5]));
-              w0.w = pack_bf16(__uint_as_float(v[6]), __uint_as_float(v[7]));
-              w1.x = pack_bf16(__uint_as_float(v[8]), __uint_as_float(v[9]));
-              w1.y = pack_bf16(__uint_as_float(v[10]), __uint_as_float(v[11]));
-              w1.z = pack_bf16(__uint_as_float(v[12]), __uint_as_float(v[13]));
-              w1.w = pack_bf16(__uint_as_float(v[14]), __uint_as_float(v[15]));
+              w0.x = pack16<F16>(__uint_as_float(v[0]), __uint_as_float(v[1]));
+              w0.y = pack16<F16>(__uint_as_float(v[2]), __uint_as_float(v[3]));
+              w0.z = pack16<F16>(__uint_as_float(v[4]), __uint_as_float(v[5]));
+              w0.w = pack16<F16>(__uint_as_float(v[6]), __uint_as_float(v[7]));
+              w1.x = pack16<F16>(__uint_as_float(v[8]), __uint_as_float(v[9]));
+              w1.y = pack16<F16>(__uint_as_float(v[10]), __uint_as_float(v[11]));
+              w1.z = pack16<F16>(__uint_as_float(v[12]), __uint_as_float(v[13]));
+              w1.w = pack16<F16>(__uint_as_float(v[14]), __uint_as_float(v[15]));
               uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
               d4[0] = w0;
               d4[1] = w1;
@@ -825,7 +825,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // (bh, n, d) bf16 row-major tensor, box = 64 columns x `rows` rows of one head, 128-byte swizzle.
-int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows) {
+int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, bool f16) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_cuda_error_text("cuTensorMapEncodeTiled entry point not available");
@@ -835,7 +835,7 @@ int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows) {
   cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(n) * d * 2};
   cuuint32_t box[3] = {64, static_cast<cuuint32_t>(rows), 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
@@ -854,10 +854,10 @@ int env_int(const char* name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-template <int PASS, int D, int BN, bool FUSED = false>
+template <int PASS, int D, int BN, bool FUSED = false, bool F16 = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, D, BN>;
-  constexpr auto kernel = tc_pass_kernel<PASS, D, BN, FUSED>;
+  constexpr auto kernel = tc_pass_kernel<PASS, D, BN, FUSED, F16>;
   RowVectors rv = row_vectors(p);
   TcParams tp;
   memset(&tp, 0, sizeof(tp));
@@ -865,16 +865,16 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   const void* k_side[4] = {p.k, p.ddk, p.v, p.ddv};
   int st = FHOB_OK;
   if (PASS != 4) {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, D, BM);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, D, BN);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, D, BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, D, BN, F16);
   } else {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, D, BM);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, BN);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, D, BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, BN, F16);
   }
   if (st != FHOB_OK) return st;
   tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
-  tp.out0 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.dq2 : p.dk2);
-  tp.out1 = static_cast<__nv_bfloat16*>(PASS == 3 ? p.ddo : p.dv2);
+  tp.out0 = static_cast<uint16_t*>(PASS == 3 ? p.dq2 : p.dk2);
+  tp.out1 = static_cast<uint16_t*>(PASS == 3 ? p.ddo : p.dv2);
   tp.status = rv.status;
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = PASS == 4 ? p.n_k : p.n_q;
@@ -906,15 +906,15 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   return FHOB_OK;
 }
 
-template <int D>
+template <int D, bool F16>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
   static const int bn1 = env_int("FHOB_TC_BN1", 128);
   switch (pass) {
-    case 1: return bn1 == 64 ? launch<1, D, 64>(p, s) : launch<1, D, 128>(p, s);
-    case 2: return launch<2, D, 64>(p, s);
-    case 12: return launch<2, D, 64, true>(p, s);  // passes 1 and 2 in one sweep
-    case 3: return launch<3, D, 64>(p, s);
-    case 4: return launch<4, D, 64>(p, s);
+    case 1: return bn1 == 64 ? launch<1, D, 64, false, F16>(p, s) : launch<1, D, 128, false, F16>(p, s);
+    case 2: return launch<2, D, 64, false, F16>(p, s);
+    case 12: return launch<2, D, 64, true, F16>(p, s);  // passes 1 and 2 in one sweep
+    case 3: return launch<3, D, 64, false, F16>(p, s);
+    case 4: return launch<4, D, 64, false, F16>(p, s);
   }
   return FHOB_ERR_ARG;
 }
@@ -922,7 +922,7 @@ int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
 }  // namespace
 
 bool tc_supported(const FhobProblem& p) {
-  return p.dtype == FHOB_BF16 && (p.d == 64 || p.d == 128) && (p.n_q % 4 == 0);
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (p.n_q % 4 == 0);
 }
 
 int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
@@ -936,7 +936,8 @@ int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
     if (major != 10) return FHOB_ERR_ARCH;
     checked_dev = dev;
   }
-  return p.d == 64 ? dispatch<64>(pass, p, s) : dispatch<128>(pass, p, s);
+  if (p.dtype == FHOB_F16) return p.d == 64 ? dispatch<64, true>(pass, p, s) : dispatch<128, true>(pass, p, s);
+  return p.d == 64 ? dispatch<64, false>(pass, p, s) : dispatch<128, false>(pass, p, s);
 }
 
 }  // namespace fhob

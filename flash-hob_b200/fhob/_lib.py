@@ -9,7 +9,8 @@ import os
 # FHOB_LIB_PATH points at an alternative build of the same library (e.g. an instrumented one)
 LIB_PATH = Path(os.environ.get("FHOB_LIB_PATH") or Path(__file__).resolve().parent / "libfhob.so")
 
-FHOB_BF16, FHOB_F32 = 0, 1
+FHOB_BF16, FHOB_F32, FHOB_F16 = 0, 1, 2
+DTYPES = {"torch.bfloat16": FHOB_BF16, "torch.float32": FHOB_F32, "torch.float16": FHOB_F16}
 IMPL = {"auto": 0, "simt": 1, "tcgen05": 2}
 ERR_TIMEOUT, ERR_SMEM_ALIGN = 64, 128
 

@@ -62,8 +62,8 @@ class _Problem:
         dev, dt = Q.device, Q.dtype
         if dev.type != "cuda":
             raise ValueError("device tensors expected (use flash_bwdbwd, which stages host tensors)")
-        if dt not in (torch.bfloat16, torch.float32):
-            raise TypeError(f"dtype {dt} not supported: bfloat16 or float32")
+        if str(dt) not in _lib.DTYPES:
+            raise TypeError(f"dtype {dt} not supported: bfloat16, float16 or float32")
         for n, t in zip(names, tensors):
             if t.device != dev:
                 raise ValueError(f"{n} is on {t.device}, Q is on {dev}")
@@ -90,7 +90,7 @@ class _Problem:
         self.ws = _workspace(dev, self.stream, nbytes)
         p = _lib.FhobProblem()
         p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
-        p.dtype = _lib.FHOB_BF16 if dt == torch.bfloat16 else _lib.FHOB_F32
+        p.dtype = _lib.DTYPES[str(dt)]
         p.causal = 1 if is_causal else 0
         p.window = _window(is_causal, window)
         p.impl = _lib.IMPL[impl]
@@ -131,8 +131,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
 
     Same positional signature and return order as the reference
     (fhog/triton_bwdbwd.py:558, :648).  Tensors are ``(BH, N, D)`` like the
-    reference or ``(B, H, N, D)``; bfloat16 (tensor-core kernels, fp32
-    accumulation) or float32 (CUDA-core kernels).  ``L`` is the logsumexp of
+    reference or ``(B, H, N, D)``; bfloat16 or float16 (tensor-core kernels,
+    fp32 accumulation) or float32 (CUDA-core kernels).  ``L`` is the logsumexp of
     the masked scaled scores, any float dtype (used as fp32).
 
     Keyword-only additions, all behaviour-preserving by default:
@@ -207,8 +207,8 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     """
     shape_q = Q.shape
     q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
-    if q.device.type != "cuda" or q.dtype not in (torch.bfloat16, torch.float32):
-        raise ValueError("attention_forward needs CUDA bfloat16/float32 tensors")
+    if q.device.type != "cuda" or str(q.dtype) not in _lib.DTYPES:
+        raise ValueError("attention_forward needs CUDA bfloat16/float16/float32 tensors")
     bh, n_q, d = q.shape
     if scale is None:
         scale = d ** -0.5
@@ -216,7 +216,7 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     lse = torch.empty(bh, n_q, dtype=torch.float32, device=q.device)
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
-    p.dtype = _lib.FHOB_BF16 if q.dtype == torch.bfloat16 else _lib.FHOB_F32
+    p.dtype = _lib.DTYPES[str(q.dtype)]
     p.causal, p.impl, p.scale = (1 if is_causal else 0), 0, float(scale)
     p.window = _window(is_causal, sliding_window)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()

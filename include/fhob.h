@@ -27,7 +27,8 @@ extern "C" {
 #endif
 
 /* Element types of the eleven matrices (all share one type). */
-enum { FHOB_BF16 = 0, FHOB_F32 = 1 };
+/* FHOB_F16: the reference's benchmark dtype (fhog/benchhhh.py:19); tensor-core path like bf16 */
+enum { FHOB_BF16 = 0, FHOB_F32 = 1, FHOB_F16 = 2 };
 
 /* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for bf16,
  * fp32 CUDA-core kernels for fp32.  SIMT forces the CUDA-core kernels for
@@ -61,7 +62,7 @@ typedef struct FhobProblem {
   int32_t n_q;     /* query rows per head */
   int32_t n_k;     /* key rows per head */
   int32_t d;       /* head dim, shared by q/k and v like the reference (:577) */
-  int32_t dtype;   /* FHOB_BF16 or FHOB_F32 */
+  int32_t dtype;   /* FHOB_BF16, FHOB_F16 or FHOB_F32 */
   int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j */
   int32_t impl;    /* FHOB_IMPL_* */
   float scale;     /* softmax scale */

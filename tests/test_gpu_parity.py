@@ -293,7 +293,8 @@ def test_wrong_inputs_raise():
     with pytest.raises(ValueError):
         fhob.flash_bwdbwd(q, q, q, q, q, q, q, q, L[:, :64], 0.125)
     with pytest.raises(TypeError):
-        fhob.flash_bwdbwd(q.half(), q.half(), q.half(), q.half(), q.half(), q.half(), q.half(), q.half(), L, 0.125)
+        qd = q.double()
+        fhob.flash_bwdbwd(qd, qd, qd, qd, qd, qd, qd, qd, L, 0.125)
     q32 = torch.zeros(2, 128, 32, device="cuda", dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="shape not supported"):
         fhob.flash_bwdbwd(q32, q32, q32, q32, q32, q32, q32, q32, L, 0.125, impl="tcgen05")
@@ -418,3 +419,34 @@ def test_sliding_window_argument_errors():
         fhob.flash_bwdbwd(*args, is_causal=True, sliding_window=0)
     with pytest.raises(ValueError):
         fhob.flash_bwdbwd(*args, is_causal=True, sliding_window=2.5)
+
+
+# ---- float16 storage (the dtype of the reference's benchmark script, fhog/benchhhh.py:19)
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,nq,nk,d", [(2, 256, 384, 64), (2, 384, 384, 128), (1, 200, 328, 128)])
+def test_fp16_outputs(bh, nq, nk, d, causal, impl):
+    x = make_inputs(bh, nq, nk, d, seed=111, dtype=torch.float64)
+    # the oracle sees the fp16-rounded inputs, like the operator
+    x = {k: v.half().double() for k, v in x.items()}
+    got, ref, _ = _run(x, d ** -0.5, causal, torch.float16, impl)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert g.dtype == torch.float16
+        assert O.rel_err(g, r) < 5e-3, n      # 11-bit significand: tighter than the bf16 bound
+
+
+def test_fp16_forward_backward_autograd():
+    import fhob
+    x = make_inputs(2, 128, 256, 64, seed=113, dtype=torch.float64)
+    x = {k: v.half().double() for k, v in x.items()}
+    ref = O.bwdbwd_autograd(*x.values(), 0.125, True)
+    q, k, v, do = (x[n].half().cuda().requires_grad_(True) for n in ("q", "k", "v", "do"))
+    out = fhob.attention(q, k, v, 0.125, is_causal=True)
+    assert out.dtype == torch.float16
+    assert O.rel_err(out.detach(), O.attn_fwd(x["q"], x["k"], x["v"], 0.125, True)) < 2e-3
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), do, create_graph=True)
+    cot = tuple(x[n].half().cuda() for n in ("ddq", "ddk", "ddv"))
+    got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < 1e-2, n
