@@ -450,3 +450,26 @@ def test_fp16_forward_backward_autograd():
     got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert O.rel_err(g, r) < 1e-2, n
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_reproduce_one_gpu_bit_for_bit():
+    """Head shards on two devices driven from one process give exactly the rows one device gives:
+    no collective, no peer access, and each call runs on the device of its tensors."""
+    import fhob
+    from fhob.sharding import sharded_call
+    x = make_inputs(6, 256, 384, 128, seed=121, dtype=torch.bfloat16, device="cuda:0")
+    scale = 128 ** -0.5
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=True)
+    names = ("q", "k", "v", "o", "do", "ddq", "ddk", "ddv", "lse")
+    full = dict(x, o=o, lse=lse)
+    ref = fhob.flash_bwdbwd(*(full[n] for n in names), scale, is_causal=True, check=True)
+    for rank in range(2):
+        dev = torch.device("cuda", rank)
+        moved = [full[n].to(dev) for n in names]
+        start, count, got = sharded_call(
+            lambda *t: fhob.flash_bwdbwd(*t, scale, is_causal=True, check=True), moved, 6, 2, rank)
+        assert count == 3
+        for g, r in zip(got, ref):
+            assert g.device == dev
+            assert torch.equal(g.cpu(), r[start:start + count].cpu())
