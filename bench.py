@@ -60,6 +60,29 @@ KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1>",
                 "pass3": "tc_pass_kernel<3, {d}, 64, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0>"}
 
 
+_JSON_FD = None
+
+
+def claim_stdout():
+    """stdout must carry exactly one JSON line, but native libraries write there too (NCCL prints
+    its version banner to file descriptor 1).  Keep a private copy of the real stdout for the JSON
+    line and point descriptor 1, and with it everything else, at stderr."""
+    global _JSON_FD
+    if _JSON_FD is None:
+        sys.stdout.flush()
+        _JSON_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line: dict):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
+
+
 def pairs(w):
     if w["causal"]:
         assert w["n_q"] == w["n_k"]
@@ -178,7 +201,7 @@ def run_reference(args, w, rank):
                 e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 note="reference XLA double-backward cannot run (jax is not installed); this is the CPU oracle "
                      "port of jax.vjp(attn_bwd) on the box's host cores")
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def mem_sweep():
@@ -230,6 +253,7 @@ def main():
     if args.mem_sweep:
         mem_sweep()
         return
+    claim_stdout()
     w = dict(WORKLOADS[args.workload])
     if args.heads > 0:
         w["bh"] = args.heads
@@ -385,7 +409,7 @@ def main():
         flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * EXEC_OVER_ALG),
         passes=passes, roofline=roofline, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
         gpu_launches=4 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
-    print(json.dumps(line), flush=True)
+    emit(line)
     if world > 1:
         dist.destroy_process_group()
 
