@@ -244,6 +244,7 @@ def main():
     ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-producers", action="store_true", help="do not time the forward / first-backward kernels")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
     ap.add_argument("--heads", type=int, default=0, help="heads per GPU (default: the workload's); "
                     "smaller values give the small cases profiler captures need")
@@ -369,6 +370,29 @@ def main():
                     flops_basis=f"{GEMM_UNITS[dom]} contractions of 2*BH*pairs*D flop issued by this pass",
                     traffic=per_head * w["bh"] if per_head else None)
 
+    # ---- the producers either side of the operator (forward: O and L; first backward: dQ, dK, dV),
+    # outside the timed region; algorithmic counts: 2 and 5 contractions of 2*BH*pairs*D flop
+    producers = None
+    if not args.no_producers:
+        from fhob.autograd import attention_backward
+        def timed(fn, reps=5):
+            fn()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps
+        ms_f = timed(lambda: fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=w["causal"]))
+        ms_b = timed(lambda: attention_backward(x["q"], x["k"], x["v"], o, x["do"], lse, scale,
+                                                is_causal=w["causal"]))
+        producers = dict(
+            forward=dict(ms=round(ms_f, 4), tflops_alg=round(2 * unit_flops / (ms_f * 1e-3) / 1e12, 1),
+                         executed_contractions=3, kernels="fo_kernel<0,..> (log-sum-exp) + fo_kernel<1,..> (P V)"),
+            first_backward=dict(ms=round(ms_b, 4), tflops_alg=round(5 * unit_flops / (ms_b * 1e-3) / 1e12, 1),
+                                executed_contractions=7, kernels="prepass + fo_kernel<2,..> (dQ) + fo_kernel<3,..> (dK, dV)"))
+
     # ---- end to end through the public entry point with host buffers
     e2e = None
     if not args.no_e2e:
@@ -407,7 +431,7 @@ def main():
                      frac_bf16_peak_exec=value / world * EXEC_OVER_ALG / peaks["burst"],
                      frac_bf16_sustained_exec=value / world * EXEC_OVER_ALG / peaks["sustained"]),
         flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * EXEC_OVER_ALG),
-        passes=passes, roofline=roofline, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
+        passes=passes, roofline=roofline, producers=producers, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
         gpu_launches=4 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
     emit(line)
     if world > 1:

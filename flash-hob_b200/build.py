@@ -14,8 +14,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OUT = HERE / "fhob" / "libfhob.so"
-SOURCES = ["fhob_api.cu", "simt_kernels.cu", "tc_kernels.cu", "static_scratch.cu"]
-HEADERS = ["fhob_common.cuh", "sm100_ptx.cuh", "../../include/fhob.h"]
+SOURCES = ["fhob_api.cu", "simt_kernels.cu", "tc_kernels.cu", "tc_first_order.cu", "static_scratch.cu"]
+HEADERS = ["fhob_common.cuh", "sm100_ptx.cuh", "tc_common.cuh", "../../include/fhob.h"]
 
 
 def nvcc_path() -> str:

@@ -223,7 +223,19 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->window < 0 || (p->window > 0 && p->causal != 1)) return FHOB_ERR_ARG;
-  return simt_forward(*p, o_out, lse_out, static_cast<cudaStream_t>(stream));
+  if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc_ok = aligned16(p->q) && aligned16(p->k) && aligned16(p->v) && aligned16(o_out) &&
+                     tc_first_order_supported(*p);
+  if (p->impl == FHOB_IMPL_TCGEN05 && !tc_ok) return FHOB_ERR_SHAPE;
+  if (p->impl != FHOB_IMPL_SIMT && tc_ok) {
+    if (p->workspace) {
+      if ((reinterpret_cast<uintptr_t>(p->workspace) & 255u) || p->workspace_bytes < sizeof(int)) return FHOB_ERR_WORKSPACE;
+      FHOB_CUDA_OK(cudaMemsetAsync(p->workspace, 0, sizeof(int), s));  // status word
+    }
+    return tc_forward(*p, o_out, lse_out, s);
+  }
+  return simt_forward(*p, o_out, lse_out, s);
 }
 
 int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stream) {
@@ -233,7 +245,9 @@ int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stre
   if (!aligned16(dq) || !aligned16(dk) || !aligned16(dv)) return FHOB_ERR_ALIGN;
   st = run_prepass(p, stream);  // stores -L*log2(e) and -D in the workspace
   if (st != FHOB_OK) return st;
-  return simt_backward(*p, dq, dk, dv, static_cast<cudaStream_t>(stream));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tc = p->impl == FHOB_IMPL_TCGEN05 || (p->impl == FHOB_IMPL_AUTO && tc_first_order_supported(*p));
+  return tc ? tc_backward(*p, dq, dk, dv, s) : simt_backward(*p, dq, dk, dv, s);
 }
 
 }  // extern "C"

@@ -1,0 +1,559 @@
+// Forward and first backward of attention on the tensor cores (sm_100a): the producers of the
+// tensors the double-backward operator consumes (O, L) and the first-order half of a
+// twice-differentiable attention function (dQ, dK, dV).  Role of the reference's forward kernel
+// and of its dense backward (fhog/triton_flash.py:12-133, :190-220), at O(N) memory.
+//
+// Same building blocks as the double-backward kernels: TMA tile loads, tcgen05.mma with fp32
+// accumulators in TMEM, elementwise math on tcgen05.ld'ed registers, 16-bit tiles written back
+// to TMEM as the A operand of the output products.  The pipeline is simpler, because TMEM has
+// room for two score stages in every mode: the issuing warp runs one tile ahead,
+//     scores(t+1) -> stage (t+1)%2 | wait for the 16-bit tiles of t | outputs(t) from stage t%2,
+// and MMAs execute in issue order, so stage t%2 is only overwritten by scores(t+2) after
+// outputs(t) have read it.
+//
+//   LSE  (queries stationary, 128 keys per tile): S = Q K^T; online log-sum-exp -> L (fp32)
+//   FWD  (queries stationary, 128 keys per tile): P = exp(S*scale - L);  O += P V
+//   BQ   (queries stationary,  64 keys per tile): dS = P (dP - D), dP = dO V^T;  dQ += dS K
+//   BK   (keys stationary,  64 queries per tile): transposed tiles;  dV += P^T dO, dK += dS^T Q
+// The forward runs LSE then FWD (the scores are computed twice, no accumulator is ever rescaled
+// and the result does not depend on the order in which tiles are visited); the backward follows
+// jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
+#include "tc_common.cuh"
+
+namespace fhob {
+namespace {
+
+enum { FO_LSE = 0, FO_FWD = 1, FO_BQ = 2, FO_BK = 3 };
+constexpr int FO_TAIL = 2048;  // barriers, TMEM base, abort flag, (max, sum) exchange
+
+template <int MODE, int D>
+struct FoCfg {
+  static constexpr bool kQStat = MODE != FO_BK;
+  static constexpr int BN = MODE <= FO_FWD ? 128 : 64;
+  static constexpr int NSTAT = MODE <= FO_FWD ? 1 : 2;   // Q | Q | Q, dO | K, V
+  static constexpr int NSTRM = MODE == FO_LSE ? 1 : 2;   // K | K, V | K, V | Q, dO
+  static constexpr int NACC = MODE <= FO_FWD ? 1 : 2;    // score tiles of a stage: S | S | S, dP | S^T, dP^T
+  static constexpr int NOUT = MODE == FO_LSE ? 0 : (MODE == FO_BK ? 2 : 1);
+  static constexpr int OUT_COLS = NOUT * D;
+  static constexpr int STAGE_COLS = NACC * BN;
+  static constexpr int STAT_BYTES = BM * D * 2;
+  static constexpr int STRM_BYTES = BN * D * 2;
+  // BK: -L*log2e and -D of the streamed queries travel with the slot
+  static constexpr int VEC_BYTES = MODE == FO_BK ? 2 * BN * 4 : 0;
+  static constexpr int TX_BYTES = NSTRM * STRM_BYTES + VEC_BYTES;
+  static constexpr int SLOT_BYTES = NSTRM * STRM_BYTES + (VEC_BYTES ? 1024 : 0);  // tiles stay 1024-byte aligned
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - FO_TAIL - NSTAT * STAT_BYTES) / SLOT_BYTES;
+  static constexpr int NSLOT = NSLOT_FIT > 4 ? 4 : NSLOT_FIT;
+  static constexpr int SMEM_BYTES = NSTAT * STAT_BYTES + NSLOT * SLOT_BYTES + FO_TAIL;
+  static_assert(OUT_COLS + 2 * STAGE_COLS <= TMEM_COLS, "TMEM budget");
+  static_assert(NSLOT >= 2, "need two streamed slots");
+  static_assert(D == 64 || D == 128, "head dim");
+};
+
+struct FoParams {
+  CUtensorMap stat[2];
+  CUtensorMap strm[2];
+  const float* lse;   // FWD: L (natural log) of the stationary queries
+  const float* nlc;   // BQ, BK: -L*log2(e) per query
+  const float* k1;    // BQ, BK: -D per query
+  float* lse_out;     // LSE
+  uint16_t* out0;     // FWD: O;  BQ: dQ;  BK: dK
+  uint16_t* out1;     // BK: dV
+  int* status;
+  int n_q, n_k, causal, window, tiles_per_head;
+  float scale;
+};
+
+struct FoBars {
+  uint64_t stat_full;
+  uint64_t strm_full[4];
+  uint64_t strm_free[4];
+  uint64_t s_full[2];   // scores of a stage finished
+  uint64_t s_free[2];   // LSE: stage read by the elementwise warps
+  uint64_t p_full[2];   // 16-bit tiles of a stage written
+  uint64_t out_full;
+  uint64_t teardown;
+  uint32_t tmem_base;
+  int abort_flag;
+  float red[2][BM];     // LSE: exchange of (max, sum) between the two column halves
+};
+static_assert(sizeof(FoBars) <= FO_TAIL, "tail");
+
+// status word used when the caller passes no workspace
+__device__ int g_fo_status;
+
+template <int MODE, int D, bool F16>
+__global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__ FoParams p) {
+  using C = FoCfg<MODE, D>;
+  constexpr bool kQStat = C::kQStat;
+  constexpr int BN = C::BN;
+  constexpr int CPT = BN / 2;  // fp32 columns of a score tile per elementwise thread
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* stat_tiles = smem;
+  uint8_t* strm_tiles = smem + C::NSTAT * C::STAT_BYTES;
+  FoBars* bars = reinterpret_cast<FoBars*>(strm_tiles + C::NSLOT * C::SLOT_BYTES);
+  int* status = p.status ? p.status : &g_fo_status;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x / p.tiles_per_head;
+  const int tile_in_head = blockIdx.x - head * p.tiles_per_head;
+  const int tile = kQStat ? p.tiles_per_head - 1 - tile_in_head : tile_in_head;  // causal: longest first
+  const int m0 = tile * BM;
+  const int n_stat = kQStat ? p.n_q : p.n_k;
+  const int n_strm = kQStat ? p.n_k : p.n_q;
+  const int off = p.n_k - p.n_q;
+  int t_begin, t_end;
+  visible_tiles(kQStat, m0, BM, BN, n_strm, off, p.causal, p.window, t_begin, t_end);
+  const int n_iter = t_end - t_begin;
+
+  if (threadIdx.x == 0) {
+    if (smem_u32(smem) & 1023u) atomicOr(status, FHOB_ERR_SMEM_ALIGN);
+    mbar_init(&bars->stat_full, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&bars->strm_full[i], 1);
+      mbar_init(&bars->strm_free[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_free[i], EW_THREADS);
+      mbar_init(&bars->p_full[i], EW_THREADS);
+    }
+    mbar_init(&bars->out_full, 1);
+    mbar_init(&bars->teardown, 1);
+    bars->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(&bars->tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == TMA_WARP && lane == 0) {
+    for (int i = 0; i < C::NSTAT; ++i) prefetch_tensormap(&p.stat[i]);
+    for (int i = 0; i < C::NSTRM; ++i) prefetch_tensormap(&p.strm[i]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // the CTA allocates all 512 columns, so the allocation starts at column 0 (checked)
+  constexpr uint32_t tmem_base = 0;
+  if (threadIdx.x == 0 && *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base) != 0)
+    atomicOr(status, FHOB_ERR_TMEM_BASE);
+
+  if (warp == TMA_WARP) {
+    // ================================================= TMA producer
+    if (lane == 0 && n_iter > 0) {
+      mbar_arrive_expect_tx(&bars->stat_full, C::NSTAT * C::STAT_BYTES);
+      for (int i = 0; i < C::NSTAT; ++i)
+        for (int bx = 0; bx < D / 64; ++bx)
+          tma_load_3d(stat_tiles + i * C::STAT_BYTES + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
+                      head);
+      int issued = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        const int slot = it % C::NSLOT;
+        if (!wait_bar(&bars->strm_free[slot], ((it / C::NSLOT) & 1) ^ 1, bars, status)) break;
+        mbar_arrive_expect_tx(&bars->strm_full[slot], C::TX_BYTES);
+        uint8_t* dst = strm_tiles + slot * C::SLOT_BYTES;
+        const int n0 = (t_begin + it) * BN;
+        for (int i = 0; i < C::NSTRM; ++i)
+          for (int bx = 0; bx < D / 64; ++bx)
+            tma_load_3d(dst + i * C::STRM_BYTES + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
+                        head);
+        if (MODE == FO_BK) {
+          const size_t vo = static_cast<size_t>(head) * p.n_q + n0;
+          uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
+          bulk_load(sv, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
+          bulk_load(sv + BN * 4, p.k1 + vo, BN * 4, &bars->strm_full[slot]);
+        }
+        issued = it + 1;
+      }
+      // drain: every load issued above must have landed before the CTA may exit
+      wait_bar(&bars->stat_full, 0, bars, status);
+      for (int it = issued > C::NSLOT ? issued - C::NSLOT : 0; it < issued; ++it) {
+        const int slot = it % C::NSLOT;
+        const long long start = clock64();
+        while (!mbar_try_wait(&bars->strm_full[slot], (it / C::NSLOT) & 1)) {
+          if (clock64() - start > kTimeoutCycles) {
+            atomicOr(status, FHOB_ERR_TIMEOUT);
+            break;
+          }
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    // ================================================= MMA issuer (whole warp runs the loop, one lane issues)
+    if (n_iter > 0) {
+      const bool leader = lane == 0;
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, wait_bar(bar, parity, bars, status)) != 0;
+      };
+      auto commit = [&](uint64_t* bar) {
+        if (leader) umma_commit(bar);
+      };
+      constexpr uint32_t idesc_s = umma_idesc_bf16(BM, BN, false, false, F16);
+      constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true, F16);
+      constexpr int kStatBox = BM * 128, kStrmBox = BN * 128;
+      const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
+      const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
+      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4, kStrm16 = C::STRM_BYTES >> 4;
+      // MN-major view of streamed tile i: leading byte offset = distance between its two 64-column boxes
+      auto mn_lo = [&](uint32_t slot_lo, int i) {
+        return slot_lo - (1u << 16) + i * kStrm16 + (static_cast<uint32_t>(kStrmBox >> 4) << 16);
+      };
+      bool ok = wait_all(&bars->stat_full, 0);
+
+      auto scores = [&](int it) -> bool {
+        const int slot = it % C::NSLOT, stage = it & 1;
+        if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
+        if (MODE == FO_LSE && !wait_all(&bars->s_free[stage], ((it >> 1) & 1) ^ 1)) return false;
+        tc_fence_after();
+        const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+        const uint32_t sl = strm_lo + slot * kSlot16;
+        gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);                             // S
+        if (C::NACC == 2) gemm_ss<D, kStatBox, kStrmBox>(leader, acc + BN, stat_lo + kStat16, sl + kStrm16, idesc_s, false);  // dP
+        commit(&bars->s_full[stage]);
+        if (MODE == FO_LSE) commit(&bars->strm_free[slot]);
+        return true;
+      };
+
+      ok = ok && scores(0);
+      for (int it = 0; ok && it < n_iter; ++it) {
+        if (it + 1 < n_iter) {
+          ok = scores(it + 1);
+          if (!ok) break;
+        }
+        if (MODE != FO_LSE) {
+          const int slot = it % C::NSLOT, stage = it & 1;
+          ok = wait_all(&bars->p_full[stage], (it >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+          const uint32_t sl = strm_lo + slot * kSlot16;
+          const bool accum = it > 0;
+          if (MODE == FO_FWD) {
+            gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
+          } else if (MODE == FO_BQ) {
+            gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
+          } else {
+            gemm_ts<D, BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
+            gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
+          }
+          commit(&bars->strm_free[slot]);
+        }
+      }
+      if (ok) {
+        if (MODE != FO_LSE) commit(&bars->out_full);
+      } else {
+        // abort path: no tcgen05.mma may still be reading shared memory or TMEM at exit
+        commit(&bars->teardown);
+        const long long start = clock64();
+        while (!mbar_try_wait(&bars->teardown, 0)) {
+          if (clock64() - start > kTimeoutCycles) break;
+        }
+      }
+    }
+  } else if (warp >= EW_WARP0) {
+    // ================================================= elementwise warps
+    const int quad = warp & 3, half = (warp - EW_WARP0) >> 2;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int g_row = m0 + row;  // stationary row of this thread
+    const float sl2 = p.scale * kLog2e;
+    float r_nlc = 0.f, r_k1 = 0.f;
+    if (kQStat && g_row < p.n_q) {
+      const size_t vi = static_cast<size_t>(head) * p.n_q + g_row;
+      if (MODE == FO_FWD) r_nlc = -p.lse[vi] * kLog2e;
+      if (MODE == FO_BQ) {
+        r_nlc = p.nlc[vi];
+        r_k1 = p.k1[vi];
+      }
+    }
+    // visible streamed index range of this thread's row
+    int lo, hi;
+    if (kQStat) {
+      lo = 0;
+      hi = p.n_k - 1;
+      if (p.causal && g_row + off < hi) hi = g_row + off;
+      if (p.window > 0 && g_row + off - p.window + 1 > 0) lo = g_row + off - p.window + 1;
+    } else {
+      lo = p.causal ? g_row - off : 0;
+      if (lo < 0) lo = 0;
+      hi = p.n_q - 1;
+      if (p.window > 0 && g_row - off + p.window - 1 < hi) hi = g_row - off + p.window - 1;
+    }
+    float run_m = -INFINITY, run_l = 0.f;  // LSE: running maximum (log2 domain) and sum
+    bool ok = true;
+
+    for (int it = 0; it < n_iter; ++it) {
+      const int n0 = (t_begin + it) * BN;
+      const int stage = it & 1;
+      bool masked = n0 + BN > n_strm;
+      if (p.causal) {
+        if (kQStat) masked = masked || (n0 + BN - 1 > m0 + off);
+        else masked = masked || (n0 + off < m0 + BM - 1);
+        if (p.window > 0) {
+          if (kQStat) masked = masked || (m0 + BM - 1 + off - n0 >= p.window);
+          else masked = masked || (n0 + BN - 1 + off - m0 >= p.window);
+        }
+      }
+      const int col_base = n0 + half * CPT;
+      uint32_t sv = 0;
+      if (MODE == FO_BK) {
+        // the slot's vectors were written by the TMA unit: observe its barrier before reading them
+        const int slot = it % C::NSLOT;
+        ok = __all_sync(0xffffffffu, wait_bar(&bars->strm_full[slot], (it / C::NSLOT) & 1, bars, status));
+        if (!ok) break;
+        sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::NSTRM * C::STRM_BYTES) + half * CPT * 4;
+      }
+      ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[stage], (it >> 1) & 1, bars, status));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t acc = tmem_base + lane_base + C::OUT_COLS + stage * C::STAGE_COLS + half * CPT;
+
+      if (MODE == FO_LSE) {
+        // online log-sum-exp over this thread's 64 columns of the tile, in the log2 domain
+        float tile_m = -INFINITY;
+        uint32_t x[2][32];
+        tmem_ld32(acc, x[0]);
+        tmem_ld32(acc + 32, x[1]);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(&bars->s_free[stage]);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int idx = col_base + 32 * c + j;
+            float y = __uint_as_float(x[c][j]) * sl2;
+            if (masked && !(idx >= lo && idx <= hi)) y = -INFINITY;
+            x[c][j] = __float_as_uint(y);
+            tile_m = fmaxf(tile_m, y);
+          }
+        const float new_m = fmaxf(run_m, tile_m);
+        if (new_m != -INFINITY) {
+          float2 sum = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+              sum = __fadd2_rn(sum, make_float2(ex2(__uint_as_float(x[c][j]) - new_m),
+                                                ex2(__uint_as_float(x[c][j + 1]) - new_m)));
+          run_l = run_l * ex2(run_m - new_m) + (sum.x + sum.y);
+          run_m = new_m;
+        }
+      } else if (MODE == FO_FWD) {
+        uint32_t w[2][16];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t x[32];
+          tmem_ld32(acc + 32 * c, x);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float2 arg = __ffma2_rn(f2(x[j], x[j + 1]), make_float2(sl2, sl2), make_float2(r_nlc, r_nlc));
+            float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+            if (masked) {
+              const int idx = col_base + 32 * c + j;
+              pr.x = (idx >= lo && idx <= hi) ? pr.x : 0.f;
+              pr.y = (idx + 1 >= lo && idx + 1 <= hi) ? pr.y : 0.f;
+            }
+            w[c][j / 2] = pack16<F16>(pr.x, pr.y);
+          }
+        }
+        // the 16-bit tile overwrites accumulator columns this thread has already consumed
+        tmem_st16(acc, w[0]);
+        tmem_st16(acc + 16, w[1]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[stage]);
+      } else {
+        uint32_t s[32], dp[32], w_p[16], w_ds[16];
+        tmem_ld32(acc, s);
+        tmem_ld32(acc + BN, dp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j4 = 0; j4 < 8; ++j4) {
+          float c_nlc[4], c_k1[4];
+          if (kQStat) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { c_nlc[e] = r_nlc; c_k1[e] = r_k1; }
+          } else {
+            load4(sv + (4 * j4) * 4, c_nlc);
+            load4(sv + (BN + 4 * j4) * 4, c_k1);
+          }
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int j = 4 * j4 + 2 * h;
+            const float2 arg = __ffma2_rn(f2(s[j], s[j + 1]), make_float2(sl2, sl2),
+                                          make_float2(c_nlc[2 * h], c_nlc[2 * h + 1]));
+            float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+            const float2 dpp = __fadd2_rn(f2(dp[j], dp[j + 1]), make_float2(c_k1[2 * h], c_k1[2 * h + 1]));
+            float2 ds = __fmul2_rn(pr, dpp);
+            if (masked) {
+              const int idx = col_base + j;
+              const bool ok0 = idx >= lo && idx <= hi, ok1 = idx + 1 >= lo && idx + 1 <= hi;
+              pr.x = ok0 ? pr.x : 0.f; pr.y = ok1 ? pr.y : 0.f;
+              ds.x = ok0 ? ds.x : 0.f; ds.y = ok1 ? ds.y : 0.f;
+            }
+            w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
+            if (MODE == FO_BK) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
+          }
+        }
+        tmem_st16(acc + BN, w_ds);
+        if (MODE == FO_BK) tmem_st16(acc, w_p);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[stage]);
+      }
+    }
+
+    // ---- results
+    if (MODE == FO_LSE) {
+      if (half == 1) {
+        bars->red[0][row] = run_m;
+        bars->red[1][row] = run_l;
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0 && ok && g_row < p.n_q) {
+        const float m1 = bars->red[0][row], l1 = bars->red[1][row];
+        const float m = fmaxf(run_m, m1);
+        float lse = -INFINITY;
+        if (m != -INFINITY) {
+          const float l = run_l * ex2(run_m - m) + l1 * ex2(m1 - m);
+          lse = (m + log2f(l)) * 0.6931471805599453f;
+        }
+        p.lse_out[static_cast<size_t>(head) * p.n_q + g_row] = lse;
+      }
+    } else {
+      if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, status));
+      tc_fence_after();
+      if (ok) {
+#pragma unroll
+        for (int o = 0; o < C::NOUT; ++o) {
+          uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
+                          (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
+          const float mul = (o == 0 && MODE != FO_FWD) ? p.scale : 1.f;  // dS was stored without the scale
+#pragma unroll
+          for (int ch = 0; ch < D / 32; ++ch) {
+            uint32_t v[16];
+            if (n_iter > 0) {
+              tmem_ld16(tmem_base + lane_base + o * D + half * (D / 2) + 16 * ch, v);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = 0u;
+            }
+            if (g_row < n_stat) {
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                w[j] = pack16<F16>(__uint_as_float(v[2 * j]) * mul, __uint_as_float(v[2 * j + 1]) * mul);
+              uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
+              d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int MODE, int D, bool F16>
+int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
+  using C = FoCfg<MODE, D>;
+  const void* q_side[2] = {p.q, p.d_o};
+  const void* k_side[2] = {p.k, p.v};
+  int st = FHOB_OK;
+  if (MODE != FO_BK) {
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, D, BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, D, C::BN, F16);
+  } else {
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, D, BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, C::BN, F16);
+  }
+  if (st != FHOB_OK) return st;
+  tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
+  const int n_stat = MODE == FO_BK ? p.n_k : p.n_q;
+  tp.tiles_per_head = (n_stat + BM - 1) / BM;
+  constexpr auto kernel = fo_kernel<MODE, D, F16>;
+  FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
+  if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
+  kernel<<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
+  FHOB_CUDA_OK(cudaGetLastError());
+  return FHOB_OK;
+}
+
+int check_device() {
+  static thread_local int checked_dev = -1;
+  int dev = 0;
+  FHOB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev != checked_dev) {
+    int major = 0;
+    FHOB_CUDA_OK(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return FHOB_ERR_ARCH;
+    checked_dev = dev;
+  }
+  return FHOB_OK;
+}
+
+template <int D, bool F16>
+int forward_impl(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s) {
+  FoParams tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.status = p.workspace ? static_cast<int*>(p.workspace) : nullptr;
+  tp.lse_out = lse_out;
+  int st = fo_launch<FO_LSE, D, F16>(p, tp, s);
+  if (st != FHOB_OK) return st;
+  tp.lse = lse_out;
+  tp.out0 = static_cast<uint16_t*>(o_out);
+  return fo_launch<FO_FWD, D, F16>(p, tp, s);
+}
+
+template <int D, bool F16>
+int backward_impl(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s) {
+  RowVectors rv = row_vectors(p);
+  FoParams tp;
+  memset(&tp, 0, sizeof(tp));
+  tp.status = rv.status;
+  tp.nlc = rv.nlc;
+  tp.k1 = rv.k1;
+  tp.out0 = static_cast<uint16_t*>(dq);
+  int st = fo_launch<FO_BQ, D, F16>(p, tp, s);
+  if (st != FHOB_OK) return st;
+  tp.out0 = static_cast<uint16_t*>(dk);
+  tp.out1 = static_cast<uint16_t*>(dv);
+  return fo_launch<FO_BK, D, F16>(p, tp, s);
+}
+
+}  // namespace
+
+bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p); }
+
+int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s) {
+  if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;
+  int st = check_device();
+  if (st != FHOB_OK) return st;
+  if (p.dtype == FHOB_F16)
+    return p.d == 64 ? forward_impl<64, true>(p, o_out, lse_out, s) : forward_impl<128, true>(p, o_out, lse_out, s);
+  return p.d == 64 ? forward_impl<64, false>(p, o_out, lse_out, s) : forward_impl<128, false>(p, o_out, lse_out, s);
+}
+
+int tc_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s) {
+  if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;
+  int st = check_device();
+  if (st != FHOB_OK) return st;
+  if (p.dtype == FHOB_F16)
+    return p.d == 64 ? backward_impl<64, true>(p, dq, dk, dv, s) : backward_impl<128, true>(p, dq, dk, dv, s);
+  return p.d == 64 ? backward_impl<64, false>(p, dq, dk, dv, s) : backward_impl<128, false>(p, dq, dk, dv, s);
+}
+
+}  // namespace fhob

@@ -25,14 +25,14 @@ from . import _lib
 from .ops import _fold, _Problem, attention_forward, flash_bwdbwd
 
 
-def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sliding_window=None):
+def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sliding_window=None, impl: str = "auto"):
     """First backward from the saved forward results: returns ``(dQ, dK, dV)``.
 
     Same maths as ``attn_bwd`` (jax_refs/flash_impl.py:124-173) with
     ``P = exp(S - L)`` and ``D = rowsum(dO * O)``; O(N) memory.
     """
     # the problem struct wants three cotangent tensors of the right shapes; they are not read
-    prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, "auto", need_outputs=False, window=sliding_window)
+    prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, impl, need_outputs=False, window=sliding_window)
     q, k = prob.keep[0], prob.keep[1]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(k)
     with torch.cuda.device(prob.device):

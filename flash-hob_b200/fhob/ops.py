@@ -197,13 +197,16 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8, 
             outs_host[3].reshape(shape_q))
 
 
-def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None):
+def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None,
+                      impl: str = "auto"):
     """O(N)-memory producer of the saved forward results: returns ``(O, L)``.
 
     ``O = softmax(Q K^T scale) V`` in the input dtype and the fp32 logsumexp
     ``L`` — the two tensors ``flash_bwdbwd`` consumes.  Role of the reference's
     forward kernel and ``produce_L`` (fhog/triton_flash.py:12-133, :252-258),
     which is dense, returns L in the input dtype and raises for causal masks.
+    16-bit inputs with D in {64, 128} run on the tensor cores (two sweeps: the
+    log-sum-exp, then ``exp(S - L) V``), everything else on CUDA cores.
     """
     shape_q = Q.shape
     q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
@@ -217,7 +220,9 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
     p.dtype = _lib.DTYPES[str(q.dtype)]
-    p.causal, p.impl, p.scale = (1 if is_causal else 0), 0, float(scale)
+    if impl not in _lib.IMPL:
+        raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
+    p.causal, p.impl, p.scale = (1 if is_causal else 0), _lib.IMPL[impl], float(scale)
     p.window = _window(is_causal, sliding_window)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream

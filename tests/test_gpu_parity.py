@@ -473,3 +473,41 @@ def test_two_gpus_reproduce_one_gpu_bit_for_bit():
         for g, r in zip(got, ref):
             assert g.device == dev
             assert torch.equal(g.cpu(), r[start:start + count].cpu())
+
+
+# ---- forward and first backward on both kernel families
+
+FO_CASES = [(2, 256, 384, 64), (2, 384, 384, 128), (1, 200, 328, 128), (3, 128, 512, 64), (1, 640, 640, 128)]
+
+
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+@pytest.mark.parametrize("causal,window", [(False, None), (True, None), (True, 70)])
+@pytest.mark.parametrize("bh,nq,nk,d", FO_CASES)
+def test_bf16_forward_and_first_backward(bh, nq, nk, d, causal, window, impl):
+    import fhob
+    import math
+    w = math.inf if window is None else window
+    x = make_inputs(bh, nq, nk, d, seed=131, dtype=torch.float64)
+    scale = d ** -0.5
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=w)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=w)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, causal, sliding_window_length=w)
+    dev = {k: v.bfloat16().cuda() for k, v in x.items()}
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, is_causal=causal, sliding_window=window,
+                                    impl=impl)
+    assert o.dtype == torch.bfloat16 and lse.dtype == torch.float32
+    assert O.rel_err(o, o_ref) < TOL_BF16 and O.rel_err(lse, l_ref) < 1e-5
+    got = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o_ref.bfloat16().cuda(), dev["do"],
+                                  l_ref.float().cuda(), scale, is_causal=causal, sliding_window=window, impl=impl)
+    for n, g, r in zip(("dq", "dk", "dv"), got, first_ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
+
+
+def test_tensor_core_forward_is_reproducible_and_matches_cuda_cores():
+    import fhob
+    x = make_inputs(4, 512, 768, 128, seed=133, dtype=torch.bfloat16, device="cuda")
+    a = fhob.attention_forward(x["q"], x["k"], x["v"], 0.09, is_causal=True, impl="tcgen05")
+    b = fhob.attention_forward(x["q"], x["k"], x["v"], 0.09, is_causal=True, impl="tcgen05")
+    c = fhob.attention_forward(x["q"], x["k"], x["v"], 0.09, is_causal=True, impl="simt")
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    assert O.rel_err(a[0], c[0].double()) < 1e-2 and O.rel_err(a[1], c[1].double()) < 1e-5
