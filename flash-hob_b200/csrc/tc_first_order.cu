@@ -72,7 +72,8 @@ struct FoBars {
   uint64_t s_free[2];   // LSE: stage read by the elementwise warps
   uint64_t p_full[2];   // 16-bit tiles of a stage written
   uint64_t out_full;
-  uint64_t teardown;
+  uint64_t go[2];       // BQ, BK: the outputs that read stage [i] have been issued (its dP columns may be reused)
+  uint64_t teardown[2];
   uint32_t tmem_base;
   int abort_flag;
   float red[2][BM];     // LSE: exchange of (max, sum) between the two column halves
@@ -114,12 +115,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       mbar_init(&bars->strm_free[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->s_full[i], C::NACC);  // one commit per issuing warp
       mbar_init(&bars->s_free[i], EW_THREADS);
       mbar_init(&bars->p_full[i], EW_THREADS);
+      mbar_init(&bars->go[i], 1);
+      mbar_init(&bars->teardown[i], 1);
     }
     mbar_init(&bars->out_full, 1);
-    mbar_init(&bars->teardown, 1);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -179,8 +181,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         }
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ================================================= MMA issuer (whole warp runs the loop, one lane issues)
+  } else if (warp == MMA_WARP || (warp == MMA_WARP2 && C::NACC == 2)) {
+    // ================================================= MMA issuers (whole warp runs the loop, one lane issues)
+    // Warp 0 issues the S products and the output products; in the backward modes warp 1 issues the
+    // dP products, because one thread cannot issue 52-cycle products fast enough.  Warp 1 reuses the
+    // dP columns of a stage (they hold dS by then) only after warp 0 has issued the outputs that read
+    // them: the tensor pipe runs MMAs in the order they arrive.
+    const int role = warp == MMA_WARP ? 0 : 1;
     if (n_iter > 0) {
       const bool leader = lane == 0;
       auto wait_all = [&](uint64_t* bar, uint32_t parity) {
@@ -201,52 +208,66 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       };
       bool ok = wait_all(&bars->stat_full, 0);
 
-      auto scores = [&](int it) -> bool {
-        const int slot = it % C::NSLOT, stage = it & 1;
-        if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
-        if (MODE == FO_LSE && !wait_all(&bars->s_free[stage], ((it >> 1) & 1) ^ 1)) return false;
-        tc_fence_after();
-        const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
-        const uint32_t sl = strm_lo + slot * kSlot16;
-        gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);                             // S
-        if (C::NACC == 2) gemm_ss<D, kStatBox, kStrmBox>(leader, acc + BN, stat_lo + kStat16, sl + kStrm16, idesc_s, false);  // dP
-        commit(&bars->s_full[stage]);
-        if (MODE == FO_LSE) commit(&bars->strm_free[slot]);
-        return true;
-      };
-
-      ok = ok && scores(0);
-      for (int it = 0; ok && it < n_iter; ++it) {
-        if (it + 1 < n_iter) {
-          ok = scores(it + 1);
-          if (!ok) break;
-        }
-        if (MODE != FO_LSE) {
+      if (role == 1) {
+        for (int it = 0; ok && it < n_iter; ++it) {
           const int slot = it % C::NSLOT, stage = it & 1;
-          ok = wait_all(&bars->p_full[stage], (it >> 1) & 1);
+          if (it >= 2) ok = wait_all(&bars->go[stage], ((it - 2) >> 1) & 1);
+          ok = ok && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
           if (!ok) break;
           tc_fence_after();
           const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
           const uint32_t sl = strm_lo + slot * kSlot16;
-          const bool accum = it > 0;
-          if (MODE == FO_FWD) {
-            gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
-          } else if (MODE == FO_BQ) {
-            gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
-          } else {
-            gemm_ts<D, BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
-            gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
+          gemm_ss<D, kStatBox, kStrmBox>(leader, acc + BN, stat_lo + kStat16, sl + kStrm16, idesc_s, false);  // dP
+          commit(&bars->s_full[stage]);
+        }
+      } else {
+        auto scores = [&](int it) -> bool {
+          const int slot = it % C::NSLOT, stage = it & 1;
+          if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
+          if (MODE == FO_LSE && !wait_all(&bars->s_free[stage], ((it >> 1) & 1) ^ 1)) return false;
+          tc_fence_after();
+          const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+          const uint32_t sl = strm_lo + slot * kSlot16;
+          gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);  // S
+          commit(&bars->s_full[stage]);
+          if (MODE == FO_LSE) commit(&bars->strm_free[slot]);
+          return true;
+        };
+
+        ok = ok && scores(0);
+        for (int it = 0; ok && it < n_iter; ++it) {
+          if (it + 1 < n_iter) {
+            ok = scores(it + 1);
+            if (!ok) break;
           }
-          commit(&bars->strm_free[slot]);
+          if (MODE != FO_LSE) {
+            const int slot = it % C::NSLOT, stage = it & 1;
+            ok = wait_all(&bars->p_full[stage], (it >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+            const uint32_t sl = strm_lo + slot * kSlot16;
+            const bool accum = it > 0;
+            if (MODE == FO_FWD) {
+              gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
+            } else if (MODE == FO_BQ) {
+              gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
+            } else {
+              gemm_ts<D, BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
+              gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
+            }
+            commit(&bars->strm_free[slot]);
+            if (C::NACC == 2 && leader) mbar_arrive(&bars->go[stage]);
+          }
         }
       }
       if (ok) {
-        if (MODE != FO_LSE) commit(&bars->out_full);
+        if (MODE != FO_LSE && role == 0) commit(&bars->out_full);
       } else {
         // abort path: no tcgen05.mma may still be reading shared memory or TMEM at exit
-        commit(&bars->teardown);
+        commit(&bars->teardown[role]);
         const long long start = clock64();
-        while (!mbar_try_wait(&bars->teardown, 0)) {
+        while (!mbar_try_wait(&bars->teardown[role], 0)) {
           if (clock64() - start > kTimeoutCycles) break;
         }
       }
@@ -341,12 +362,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           run_m = new_m;
         }
       } else if (MODE == FO_FWD) {
-        uint32_t w[2][16];
+        uint32_t w[2][16], xx[2][32];
+        tmem_ld32(acc, xx[0]);
+        tmem_ld32(acc + 32, xx[1]);
+        tmem_wait_ld();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t x[32];
-          tmem_ld32(acc + 32 * c, x);
-          tmem_wait_ld();
+          const uint32_t (&x)[32] = xx[c];
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
             const float2 arg = __ffma2_rn(f2(x[j], x[j + 1]), make_float2(sl2, sl2), make_float2(r_nlc, r_nlc));
