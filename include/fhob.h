@@ -162,8 +162,11 @@ int fhob_read_status(const FhobProblem* p, void* stream);
  * consumes: O = softmax(QK^T scale) V in the input element type and the fp32
  * logsumexp L.  Role of flash_kernel / produce_L in the reference
  * (fhog/triton_flash.py:12-133, :252-258), which is dense, rounds L to the
- * input type and refuses causal masks.  Uses p->q, k, v, scale, causal;
- * writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).  CUDA-core kernel.
+ * input type and refuses causal masks.  Uses p->q, k, v, scale, causal,
+ * window, impl; writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).
+ * 16-bit inputs with d in {64, 128} run on the tensor cores (impl AUTO or
+ * TCGEN05), everything else on CUDA cores.  p->workspace may be NULL; when
+ * given, its status word is cleared and receives device-side timeouts.
  */
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream);
 
@@ -175,6 +178,7 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
  * the reference (fhog/triton_flash.py:190-220), which materialises S, P, dP,
  * dS.  It is the function whose derivative fhob_bwdbwd computes
  * (jax_refs/flash_impl.py:124-173).  CUDA-core kernel.
+  * Tensor cores or CUDA cores as for fhob_forward.
  */
 int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stream);
 
