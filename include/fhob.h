@@ -177,8 +177,8 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
  * overwritten).  Role of FlashAttention2.backward / flash_backward_torch in
  * the reference (fhog/triton_flash.py:190-220), which materialises S, P, dP,
  * dS.  It is the function whose derivative fhob_bwdbwd computes
- * (jax_refs/flash_impl.py:124-173).  CUDA-core kernel.
-  * Tensor cores or CUDA cores as for fhob_forward.
+ * (jax_refs/flash_impl.py:124-173).  Tensor cores or CUDA cores as for
+ * fhob_forward.
  */
 int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stream);
 
