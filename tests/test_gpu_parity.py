@@ -511,3 +511,45 @@ def test_tensor_core_forward_is_reproducible_and_matches_cuda_cores():
     c = fhob.attention_forward(x["q"], x["k"], x["v"], 0.09, is_causal=True, impl="simt")
     assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
     assert O.rel_err(a[0], c[0].double()) < 1e-2 and O.rel_err(a[1], c[1].double()) < 1e-5
+
+
+# ---- seeded random shapes: tile-range and masking logic of every tensor-core kernel
+
+def _random_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < n:
+        d = rng.choice([64, 128])
+        nq = 4 * rng.randint(1, 110)             # the tensor-core path needs N_Q % 4 == 0
+        nk = rng.randint(1, 450)
+        causal = rng.random() < 0.6
+        if causal and nk < nq:
+            nk = nq + rng.randint(0, 64)         # every query keeps at least one visible key
+        window = rng.choice([None, None, rng.randint(1, 300)]) if causal else None
+        cases.append((rng.randint(1, 3), nq, nk, d, causal, window))
+    return cases
+
+
+@pytest.mark.parametrize("bh,nq,nk,d,causal,window", _random_cases(24, seed=2024))
+def test_random_shapes_all_tensor_core_kernels(bh, nq, nk, d, causal, window):
+    import fhob
+    import math
+    w = math.inf if window is None else window
+    x = make_inputs(bh, nq, nk, d, seed=nq * 1000 + nk, dtype=torch.float64)
+    scale = d ** -0.5
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=w)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=w)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, causal, sliding_window_length=w)
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal, sliding_window_length=w)
+    dev = {k: v.bfloat16().cuda() for k, v in x.items()}
+    kw = dict(is_causal=causal, sliding_window=window, impl="tcgen05")
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **kw)
+    assert O.rel_err(o, o_ref) < TOL_BF16 and O.rel_err(lse, l_ref) < 1e-5
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **kw)
+    for n, g, r in zip(("dq", "dk", "dv"), first, first_ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o, dev["do"], dev["ddq"], dev["ddk"], dev["ddv"], lse,
+                            scale, check=True, **kw)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
