@@ -218,6 +218,12 @@ int fhob_read_status(const FhobProblem* p, void* stream) {
   return host;
 }
 
+int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* stream) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < sizeof(int))
+    return FHOB_ERR_WORKSPACE;
+  return tc_selftest_expired_wait(static_cast<int*>(workspace), static_cast<cudaStream_t>(stream));
+}
+
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream) {
   if (!p || !p->q || !p->k || !p->v || !o_out || !lse_out) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;

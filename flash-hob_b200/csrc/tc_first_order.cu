@@ -556,7 +556,29 @@ int backward_impl(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream
   return fo_launch<FO_BK, D, F16>(p, tp, s);
 }
 
+// One warp waits on an mbarrier nothing ever arrives on: exercises the give-up branch of wait_bar.
+struct ExpireBars {
+  uint64_t bar;
+  int abort_flag;
+};
+__global__ void expire_wait_kernel(int* status) {
+  __shared__ ExpireBars b;
+  if (threadIdx.x == 0) {
+    mbar_init(&b.bar, 1);
+    b.abort_flag = 0;
+    fence_barrier_init();
+  }
+  __syncthreads();
+  wait_bar(&b.bar, 0, &b, status);
+}
+
 }  // namespace
+
+int tc_selftest_expired_wait(int* status, cudaStream_t s) {
+  expire_wait_kernel<<<1, 32, 0, s>>>(status);
+  FHOB_CUDA_OK(cudaGetLastError());
+  return FHOB_OK;
+}
 
 bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p); }
 

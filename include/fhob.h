@@ -158,6 +158,17 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
 int fhob_read_status(const FhobProblem* p, void* stream);
 
 /*
+ * Self-test of the bounded device waits.  Queues one warp whose only wait is
+ * on an mbarrier nothing ever arrives on; after about a second the wait gives
+ * up, ORs FHOB_ERR_TIMEOUT into the status word at the start of `workspace`
+ * (256-byte aligned device memory) and the kernel returns normally, so the
+ * context stays usable.  This is the path every kernel of the library takes
+ * when a wait runs out; fhob_read_status then reports it.  The reference has
+ * no counterpart.
+ */
+int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * O(N)-memory producer of the two saved forward results the operator
  * consumes: O = softmax(QK^T scale) V in the input element type and the fp32
  * logsumexp L.  Role of flash_kernel / produce_L in the reference

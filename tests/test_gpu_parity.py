@@ -553,3 +553,25 @@ def test_random_shapes_all_tensor_core_kernels(bh, nq, nk, d, causal, window):
                             scale, check=True, **kw)
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert O.rel_err(g, r) < TOL_BF16, n
+
+
+def test_expired_wait_is_reported_and_leaves_the_context_usable():
+    """A device wait that can never complete gives up after about a second, sets FHOB_ERR_TIMEOUT
+    in the status word and the kernel returns; the next operator call clears the word and works."""
+    import ctypes as C
+    import fhob
+    from fhob import _lib
+    lib = _lib.load()
+    x = make_inputs(1, 128, 128, 64, seed=141, dtype=torch.bfloat16, device="cuda")
+    ws = torch.zeros(lib.fhob_workspace_bytes(1, 128), dtype=torch.uint8, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.fhob_selftest_expired_wait(C.c_void_p(ws.data_ptr()), ws.numel(), stream) == 0
+    p = _lib.FhobProblem()
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
+    assert lib.fhob_read_status(C.byref(p), stream) == _lib.ERR_TIMEOUT
+    with pytest.raises(RuntimeError, match="status 64"):
+        _lib.check(_lib.ERR_TIMEOUT, "self-test")
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 0.125)
+    got = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 0.125,
+                            check=True)
+    assert all(torch.isfinite(g.float()).all() for g in got)
