@@ -56,8 +56,8 @@ EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # the heads, every head having its own tensors).  None for shapes that were not captured.
 DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass12"): 191.47e6 / 16,
                        ("cfg5-shard", "pass3"): 211.82e6 / 16, ("cfg5-shard", "pass4"): 229.40e6 / 16}
-KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1>",
-                "pass3": "tc_pass_kernel<3, {d}, 64, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0>"}
+KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1, 0>",
+                "pass3": "tc_pass_kernel<3, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0, 0>"}
 
 
 _JSON_FD = None
