@@ -19,6 +19,10 @@ _workspaces: dict = {}
 
 
 def _workspace(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    if torch.cuda.is_current_stream_capturing():
+        # memory allocated while a CUDA graph is captured belongs to the graph's pool: the graph
+        # keeps it alive for its replays, a cache that outlives the graph must not
+        return torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
     key = (device.index, stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:

@@ -575,3 +575,34 @@ def test_expired_wait_is_reported_and_leaves_the_context_usable():
     got = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 0.125,
                             check=True)
     assert all(torch.isfinite(g.float()).all() for g in got)
+
+
+def test_cuda_graph_capture_and_replay():
+    """The operator only queues kernels on the current stream (no synchronisation, no allocation
+    of its own on the success path), so a call can be captured into a CUDA graph and replayed on
+    new input values; replays reproduce the eager results bit for bit."""
+    import fhob
+    scale = 0.125
+    static = make_inputs(4, 256, 384, 64, seed=151, dtype=torch.bfloat16, device="cuda")
+    o, lse = fhob.attention_forward(static["q"], static["k"], static["v"], scale, is_causal=True)
+    args = lambda: (static["q"], static["k"], static["v"], o, static["do"], static["ddq"], static["ddk"],
+                    static["ddv"], lse, scale)
+    fhob.flash_bwdbwd(*args(), is_causal=True)          # warm-up outside the capture
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        o_g, lse_g = fhob.attention_forward(static["q"], static["k"], static["v"], scale, is_causal=True)
+        outs = fhob.flash_bwdbwd(static["q"], static["k"], static["v"], o_g, static["do"], static["ddq"],
+                                 static["ddk"], static["ddv"], lse_g, scale, is_causal=True)
+    for seed in (152, 153):
+        fresh = make_inputs(4, 256, 384, 64, seed=seed, dtype=torch.bfloat16, device="cuda")
+        for k in static:
+            static[k].copy_(fresh[k])
+        graph.replay()
+        torch.cuda.synchronize()
+        o_e, lse_e = fhob.attention_forward(fresh["q"], fresh["k"], fresh["v"], scale, is_causal=True)
+        eager = fhob.flash_bwdbwd(fresh["q"], fresh["k"], fresh["v"], o_e, fresh["do"], fresh["ddq"], fresh["ddk"],
+                                  fresh["ddv"], lse_e, scale, is_causal=True, check=True)
+        assert torch.equal(o_g, o_e) and torch.equal(lse_g, lse_e)
+        for g, e in zip(outs, eager):
+            assert torch.equal(g, e)
