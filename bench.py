@@ -196,7 +196,9 @@ def run_reference(args, w, rank):
     line = dict(metric="double_backward_attention_tflops", value=cb["value"], unit="TFLOP/s", impl="reference",
                 n_gpus=args.gpus, steps=reps, warmup=max(1, min(args.warmup, 2)), ms_per_step=sec * 1e3,
                 higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=args.workload, description=w["desc"], sample="1 head per step on host CPU"),
+                config=dict(workload=args.workload, description=w["desc"], bh_per_gpu=w["bh"], n_q=w["n_q"],
+                            n_k=w["n_k"], d=w["d"], causal=w["causal"],
+                            sample="each step is a bounded sample of the workload: 1 head on the host CPU"),
                 cpu_baseline=cb,
                 e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
                 note="reference XLA double-backward cannot run (jax is not installed); this is the CPU oracle "
