@@ -218,6 +218,14 @@ int fhob_read_status(const FhobProblem* p, void* stream) {
   return host;
 }
 
+int fhob_visible_tiles(int q_stationary, int m0, int rows, int tile, int n_q, int n_k, int causal, int window,
+                       int* t_begin, int* t_end) {
+  if (!t_begin || !t_end || rows <= 0 || tile <= 0 || n_q <= 0 || n_k <= 0 || m0 < 0 || window < 0) return FHOB_ERR_ARG;
+  visible_tiles(q_stationary != 0, m0, rows, tile, q_stationary ? n_k : n_q, n_k - n_q, causal, window, *t_begin,
+                *t_end);
+  return FHOB_OK;
+}
+
 int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* stream) {
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < sizeof(int))
     return FHOB_ERR_WORKSPACE;

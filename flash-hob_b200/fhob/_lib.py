@@ -19,7 +19,7 @@ SYMBOLS = (
     "fhob_version", "fhob_strerror", "fhob_last_cuda_error", "fhob_workspace_bytes", "fhob_bwdbwd",
     "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
     "fhob_read_status", "fhob_forward", "fhob_backward", "fhob_bwdbwd_static_scratch",
-    "fhob_selftest_expired_wait",
+    "fhob_selftest_expired_wait", "fhob_visible_tiles",
 )
 STATIC_SCRATCH_MAX_ROWS = 262144
 
@@ -65,6 +65,8 @@ def load() -> C.CDLL:
     lib.fhob_row_stats.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.fhob_backward.restype = C.c_int
     lib.fhob_backward.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.fhob_visible_tiles.restype = C.c_int
+    lib.fhob_visible_tiles.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]
     lib.fhob_selftest_expired_wait.restype = C.c_int
     lib.fhob_selftest_expired_wait.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
     lib.fhob_forward.restype = C.c_int

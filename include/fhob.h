@@ -158,6 +158,19 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
 int fhob_read_status(const FhobProblem* p, void* stream);
 
 /*
+ * The tile-range rule every kernel of the library uses (host evaluation, no
+ * GPU needed): for stationary rows [m0, m0 + rows) — queries if q_stationary,
+ * else keys — the half-open range [*t_begin, *t_end) of streamed tiles of
+ * `tile` rows that can hold a pair visible under the mask of
+ * jax_refs/flash_impl.py:86-91 (causal, bottom-right aligned, optional
+ * sliding window).  Exposed so that the rule can be checked exhaustively
+ * against the mask definition; the reference has no counterpart (its
+ * kernels visit every tile).
+ */
+int fhob_visible_tiles(int q_stationary, int m0, int rows, int tile, int n_q, int n_k, int causal, int window,
+                       int* t_begin, int* t_end);
+
+/*
  * Self-test of the bounded device waits.  Queues one warp whose only wait is
  * on an mbarrier nothing ever arrives on; after about a second the wait gives
  * up, ORs FHOB_ERR_TIMEOUT into the status word at the start of `workspace`

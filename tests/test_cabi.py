@@ -96,3 +96,37 @@ def test_missing_library_is_loud(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libfhob.so")
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_tile_range_rule_against_the_mask_definition(lib):
+    """Exhaustive check of the streamed-tile range the kernels visit: it must contain every tile
+    that holds a visible pair (otherwise results silently lose terms) and nothing beyond the
+    first and last such tile (otherwise work is wasted)."""
+    import itertools
+    from oracle import attn_oracle as O
+    import math
+    tb, te = C.c_int(), C.c_int()
+    checked = 0
+    for n_q, n_k, window in itertools.product((5, 16, 37), (7, 16, 50), (0, 1, 6, 23)):
+        for causal in ((1,) if window else (0, 1)):
+            mask = O.bottom_right_mask(n_q, n_k, window if window else math.inf) if causal else None
+            for rows, tile, q_stat in itertools.product((4, 16), (4, 8), (0, 1)):
+                n_stat, n_strm = (n_q, n_k) if q_stat else (n_k, n_q)
+                for m0 in range(0, n_stat, rows):
+                    assert lib.fhob_visible_tiles(q_stat, m0, rows, tile, n_q, n_k, causal, window,
+                                                  C.byref(tb), C.byref(te)) == 0
+                    want = set()
+                    for r in range(m0, min(m0 + rows, n_stat)):
+                        for c in range(n_strm):
+                            qi, kj = (r, c) if q_stat else (c, r)
+                            if mask is None or bool(mask[qi, kj]):
+                                want.add(c // tile)
+                    n_tiles = -(-n_strm // tile)
+                    assert 0 <= tb.value <= te.value <= n_tiles
+                    if want:
+                        assert tb.value <= min(want) and max(want) < te.value
+                        # rows past the end of a ragged last stationary tile may widen the range, never shrink it
+                        if m0 + rows <= n_stat:
+                            assert (tb.value, te.value) == (min(want), max(want) + 1)
+                    checked += 1
+    assert checked > 1000
