@@ -391,7 +391,7 @@ def main():
                                                 is_causal=w["causal"]))
         producers = dict(
             forward=dict(ms=round(ms_f, 4), tflops_alg=round(2 * unit_flops / (ms_f * 1e-3) / 1e12, 1),
-                         executed_contractions=3, kernels="fo_kernel<0,..> (log-sum-exp) + fo_kernel<1,..> (P V)"),
+                         executed_contractions=2, kernels="fo_kernel<4,..> (single sweep, online softmax)"),
             first_backward=dict(ms=round(ms_b, 4), tflops_alg=round(5 * unit_flops / (ms_b * 1e-3) / 1e12, 1),
                                 executed_contractions=7, kernels="prepass + fo_kernel<2,..> (dQ) + fo_kernel<3,..> (dK, dV)"))
 

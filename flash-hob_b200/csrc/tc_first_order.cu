@@ -11,28 +11,33 @@
 // and MMAs execute in issue order, so stage t%2 is only overwritten by scores(t+2) after
 // outputs(t) have read it.
 //
+//   ONE  (queries stationary, 128 keys per tile): single-sweep forward.  Online softmax against a
+//        reference maximum that follows the running row maximum lazily (only when it has grown by
+//        more than 8 in the log2 domain); on those occasions the threads rescale their part of O
+//        in TMEM, which is idle between two P V products.  Writes O and L.
 //   LSE  (queries stationary, 128 keys per tile): S = Q K^T; online log-sum-exp -> L (fp32)
 //   FWD  (queries stationary, 128 keys per tile): P = exp(S*scale - L);  O += P V
 //   BQ   (queries stationary,  64 keys per tile): dS = P (dP - D), dP = dO V^T;  dQ += dS K
 //   BK   (keys stationary,  64 queries per tile): transposed tiles;  dV += P^T dO, dK += dS^T Q
-// The forward runs LSE then FWD (the scores are computed twice, no accumulator is ever rescaled
-// and the result does not depend on the order in which tiles are visited); the backward follows
-// jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
+// The forward is ONE; with FHOB_FORWARD_TWO_SWEEPS set in the environment it runs LSE then FWD
+// instead (the scores are computed twice, but no accumulator is ever rescaled).  The backward
+// follows jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
 #include "tc_common.cuh"
 
 namespace fhob {
 namespace {
 
-enum { FO_LSE = 0, FO_FWD = 1, FO_BQ = 2, FO_BK = 3 };
-constexpr int FO_TAIL = 2048;  // barriers, TMEM base, abort flag, (max, sum) exchange
+enum { FO_LSE = 0, FO_FWD = 1, FO_BQ = 2, FO_BK = 3, FO_ONE = 4 };
+constexpr int FO_TAIL = 3072;  // barriers, TMEM base, abort flag, (max, sum) exchange
 
 template <int MODE, int D>
 struct FoCfg {
   static constexpr bool kQStat = MODE != FO_BK;
-  static constexpr int BN = MODE <= FO_FWD ? 128 : 64;
-  static constexpr int NSTAT = MODE <= FO_FWD ? 1 : 2;   // Q | Q | Q, dO | K, V
+  static constexpr bool kForward = MODE == FO_LSE || MODE == FO_FWD || MODE == FO_ONE;
+  static constexpr int BN = kForward ? 128 : 64;
+  static constexpr int NSTAT = kForward ? 1 : 2;         // Q | Q | Q, dO | K, V
   static constexpr int NSTRM = MODE == FO_LSE ? 1 : 2;   // K | K, V | K, V | Q, dO
-  static constexpr int NACC = MODE <= FO_FWD ? 1 : 2;    // score tiles of a stage: S | S | S, dP | S^T, dP^T
+  static constexpr int NACC = kForward ? 1 : 2;          // score tiles of a stage: S | S | S, dP | S^T, dP^T
   static constexpr int NOUT = MODE == FO_LSE ? 0 : (MODE == FO_BK ? 2 : 1);
   static constexpr int OUT_COLS = NOUT * D;
   static constexpr int STAGE_COLS = NACC * BN;
@@ -72,11 +77,13 @@ struct FoBars {
   uint64_t s_free[2];   // LSE: stage read by the elementwise warps
   uint64_t p_full[2];   // 16-bit tiles of a stage written
   uint64_t out_full;
+  uint64_t o_done;      // ONE: the P V product of a tile has finished (O may be rescaled)
+  uint64_t pair[4];     // ONE: the two warps that share 32 rows have both published their maximum
   uint64_t go[2];       // BQ, BK: the outputs that read stage [i] have been issued (its dP columns may be reused)
   uint64_t teardown[2];
   uint32_t tmem_base;
   int abort_flag;
-  float red[2][BM];     // LSE: exchange of (max, sum) between the two column halves
+  float red[2][2][BM];  // exchange of maxima / sums between the two column halves: [tile parity][half][row]
 };
 static_assert(sizeof(FoBars) <= FO_TAIL, "tail");
 
@@ -122,6 +129,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       mbar_init(&bars->teardown[i], 1);
     }
     mbar_init(&bars->out_full, 1);
+    mbar_init(&bars->o_done, 1);
+    for (int i = 0; i < 4; ++i) mbar_init(&bars->pair[i], 64);
     bars->abort_flag = 0;
     fence_barrier_init();
   }
@@ -181,12 +190,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         }
       }
     }
-  } else if (warp == MMA_WARP || (warp == MMA_WARP2 && C::NACC == 2)) {
+  } else if (warp == MMA_WARP || (warp == MMA_WARP2 && MODE != FO_LSE)) {
     // ================================================= MMA issuers (whole warp runs the loop, one lane issues)
-    // Warp 0 issues the S products and the output products; in the backward modes warp 1 issues the
-    // dP products, because one thread cannot issue 52-cycle products fast enough.  Warp 1 reuses the
-    // dP columns of a stage (they hold dS by then) only after warp 0 has issued the outputs that read
-    // them: the tensor pipe runs MMAs in the order they arrive.
+    // One thread cannot issue the products of a tile fast enough, so two warps share them.
+    // Backward modes: warp 0 issues the S products and the output products, warp 1 the dP products;
+    // warp 1 reuses the dP columns of a stage (they hold dS by then) only after warp 0 has issued
+    // the outputs that read them.  Forward modes with an output: warp 0 issues the S products,
+    // warp 1 the P V products; warp 0 reuses a stage (it holds P by then) only after warp 1 has
+    // issued the product that reads it.  The tensor pipe runs MMAs in the order they arrive.
+    constexpr bool kSplitOutputs = C::kForward && MODE != FO_LSE;  // warp 1 issues the outputs
     const int role = warp == MMA_WARP ? 0 : 1;
     if (n_iter > 0) {
       const bool leader = lane == 0;
@@ -208,7 +220,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       };
       bool ok = wait_all(&bars->stat_full, 0);
 
-      if (role == 1) {
+      if (kSplitOutputs) {
+        for (int it = 0; ok && it < n_iter; ++it) {
+          const int slot = it % C::NSLOT, stage = it & 1;
+          const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
+          const uint32_t sl = strm_lo + slot * kSlot16;
+          if (role == 0) {
+            if (it >= 2) ok = wait_all(&bars->go[stage], ((it - 2) >> 1) & 1);
+            ok = ok && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);  // S
+            commit(&bars->s_full[stage]);
+          } else {
+            ok = wait_all(&bars->p_full[stage], (it >> 1) & 1) && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, it > 0);  // O += P . V
+            commit(&bars->strm_free[slot]);
+            if (MODE == FO_ONE) commit(&bars->o_done);
+            if (leader) mbar_arrive(&bars->go[stage]);
+          }
+        }
+      } else if (role == 1) {
         for (int it = 0; ok && it < n_iter; ++it) {
           const int slot = it % C::NSLOT, stage = it & 1;
           if (it >= 2) ok = wait_all(&bars->go[stage], ((it - 2) >> 1) & 1);
@@ -248,8 +282,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
             const uint32_t sl = strm_lo + slot * kSlot16;
             const bool accum = it > 0;
-            if (MODE == FO_FWD) {
+            if (MODE == FO_FWD || MODE == FO_ONE) {
               gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
+              if (MODE == FO_ONE) commit(&bars->o_done);
             } else if (MODE == FO_BQ) {
               gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
             } else {
@@ -262,7 +297,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         }
       }
       if (ok) {
-        if (MODE != FO_LSE && role == 0) commit(&bars->out_full);
+        if (MODE != FO_LSE && role == (kSplitOutputs ? 1 : 0)) commit(&bars->out_full);
       } else {
         // abort path: no tcgen05.mma may still be reading shared memory or TMEM at exit
         commit(&bars->teardown[role]);
@@ -361,6 +396,78 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           run_l = run_l * ex2(run_m - new_m) + (sum.x + sum.y);
           run_m = new_m;
         }
+      } else if (MODE == FO_ONE) {
+        // single-sweep forward: online softmax with a lazily updated reference maximum.  P is
+        // formed against m_used, which follows the running row maximum only when that has grown
+        // by more than 8 (P stays below 2^8); O and the row sum are rescaled on those occasions.
+        uint32_t xx[2][32], w[2][16];
+        tmem_ld32(acc, xx[0]);
+        tmem_ld32(acc + 32, xx[1]);
+        tmem_wait_ld();
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float2 y = __fmul2_rn(f2(xx[c][j], xx[c][j + 1]), make_float2(sl2, sl2));
+            if (masked) {
+              const int idx = col_base + 32 * c + j;
+              y.x = (idx >= lo && idx <= hi) ? y.x : -INFINITY;
+              y.y = (idx + 1 >= lo && idx + 1 <= hi) ? y.y : -INFINITY;
+            }
+            xx[c][j] = __float_as_uint(y.x);
+            xx[c][j + 1] = __float_as_uint(y.y);
+            mx[(j >> 1) & 3] = fmaxf(mx[(j >> 1) & 3], fmaxf(y.x, y.y));
+          }
+        float tile_m = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        // the row's maximum over both column halves (the partner warp owns the other 64 columns)
+        bars->red[it & 1][half][row] = tile_m;
+        mbar_arrive(&bars->pair[quad]);
+        ok = __all_sync(0xffffffffu, wait_bar(&bars->pair[quad], it & 1, bars, status));
+        if (!ok) break;
+        tile_m = fmaxf(tile_m, bars->red[it & 1][half ^ 1][row]);
+        const bool need = tile_m > run_m + 8.f;   // run_m holds m_used; true for the first finite maximum
+        if (it > 0 && __any_sync(0xffffffffu, need)) {
+          // O is idle once the previous tile's P V has finished; the next one waits for this tile's P
+          ok = __all_sync(0xffffffffu, wait_bar(&bars->o_done, (it - 1) & 1, bars, status));
+          if (!ok) break;
+          tc_fence_after();
+          const float alpha = (need && run_m != -INFINITY) ? ex2(run_m - tile_m) : 1.f;
+#pragma unroll
+          for (int ch = 0; ch < D / 64; ++ch) {
+            uint32_t v[32], lo16[16], hi16[16];
+            const uint32_t addr = tmem_base + lane_base + half * (D / 2) + 32 * ch;
+            tmem_ld32(addr, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              lo16[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+              hi16[j] = __float_as_uint(__uint_as_float(v[16 + j]) * alpha);
+            }
+            tmem_st16(addr, lo16);
+            tmem_st16(addr + 16, hi16);
+          }
+          tmem_wait_st();
+          run_l *= alpha;
+        }
+        if (need) run_m = tile_m;
+        const float neg_m = run_m == -INFINITY ? 0.f : -run_m;
+        float2 sum = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float2 d = __fadd2_rn(f2(xx[c][j], xx[c][j + 1]), make_float2(neg_m, neg_m));
+            const float2 pr = make_float2(ex2(d.x), ex2(d.y));
+            sum = __fadd2_rn(sum, pr);
+            w[c][j / 2] = pack16<F16>(pr.x, pr.y);
+          }
+        run_l += sum.x + sum.y;
+        tmem_st16(acc, w[0]);
+        tmem_st16(acc + 16, w[1]);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(&bars->p_full[stage]);
       } else if (MODE == FO_FWD) {
         uint32_t w[2][16], xx[2][32];
         tmem_ld32(acc, xx[0]);
@@ -431,12 +538,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
     // ---- results
     if (MODE == FO_LSE) {
       if (half == 1) {
-        bars->red[0][row] = run_m;
-        bars->red[1][row] = run_l;
+        bars->red[0][0][row] = run_m;
+        bars->red[0][1][row] = run_l;
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (half == 0 && ok && g_row < p.n_q) {
-        const float m1 = bars->red[0][row], l1 = bars->red[1][row];
+        const float m1 = bars->red[0][0][row], l1 = bars->red[0][1][row];
         const float m = fmaxf(run_m, m1);
         float lse = -INFINITY;
         if (m != -INFINITY) {
@@ -446,6 +553,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         p.lse_out[static_cast<size_t>(head) * p.n_q + g_row] = lse;
       }
     } else {
+      float inv_l = 1.f;
+      if (MODE == FO_ONE) {
+        // row sum over both column halves; L = m_used + log(sum), O = accumulator / sum
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // every reader of the per-tile maxima is done
+        bars->red[0][half][row] = run_l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float l = run_l + bars->red[0][half ^ 1][row];
+        inv_l = l > 0.f ? 1.f / l : 0.f;
+        if (half == 0 && ok && g_row < p.n_q)
+          p.lse_out[static_cast<size_t>(head) * p.n_q + g_row] =
+              l > 0.f ? (run_m + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
       if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, status));
       tc_fence_after();
       if (ok) {
@@ -453,7 +572,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         for (int o = 0; o < C::NOUT; ++o) {
           uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
                           (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
-          const float mul = (o == 0 && MODE != FO_FWD) ? p.scale : 1.f;  // dS was stored without the scale
+          // dS was stored without the scale; the single-sweep forward divides by the row sum here
+          const float mul = MODE == FO_ONE ? inv_l : ((o == 0 && MODE != FO_FWD) ? p.scale : 1.f);
 #pragma unroll
           for (int ch = 0; ch < D / 32; ++ch) {
             uint32_t v[16];
@@ -533,10 +653,13 @@ int forward_impl(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t
   memset(&tp, 0, sizeof(tp));
   tp.status = p.workspace ? static_cast<int*>(p.workspace) : nullptr;
   tp.lse_out = lse_out;
+  tp.out0 = static_cast<uint16_t*>(o_out);
+  static const bool two_sweeps = getenv("FHOB_FORWARD_TWO_SWEEPS") != nullptr;
+  if (!two_sweeps) return fo_launch<FO_ONE, D, F16>(p, tp, s);
+  // the order-independent variant: log-sum-exp first, then exp(S - L) V
   int st = fo_launch<FO_LSE, D, F16>(p, tp, s);
   if (st != FHOB_OK) return st;
   tp.lse = lse_out;
-  tp.out0 = static_cast<uint16_t*>(o_out);
   return fo_launch<FO_FWD, D, F16>(p, tp, s);
 }
 
