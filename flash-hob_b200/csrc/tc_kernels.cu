@@ -1,11 +1,13 @@
 // Tensor-core kernels of the double-backward attention operator for sm_100a:
 // TMA tile loads -> tcgen05.mma with fp32 accumulators in TMEM -> tcgen05.ld
-// into registers for the elementwise math -> (passes 3, 4) bf16 tiles written
-// back to TMEM and used as the A operand of the output products.
+// into registers for the elementwise math -> (passes 3, 4) 16-bit tiles (bf16
+// or f16, the storage type) written back to TMEM and used as the A operand of
+// the output products.
 //
 // One kernel template covers the four passes (reference: passes 1-3 are the
 // three key loops of bwdbwd_kernel_stage1, fhog/triton_bwdbwd.py:178-313;
-// pass 4 is bwdbwd_kernel_stage2, :321-535).  A CTA owns BM = 128 "stationary"
+// pass 4 is bwdbwd_kernel_stage2, :321-535) and the sweep that replaces passes
+// 1 and 2 in the operator (FUSED: both row statistics from one recomputation).  A CTA owns BM = 128 "stationary"
 // rows of one head (queries in passes 1-3, keys in pass 4) which become the 128
 // TMEM lanes, and streams BN-row tiles of the other side:
 //

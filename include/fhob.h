@@ -108,7 +108,7 @@ const char* fhob_last_cuda_error(void);
 size_t fhob_workspace_bytes(int32_t bh, int32_t n_q);
 
 /*
- * The whole operator: row-statistics pre-pass and the four recomputation
+ * The whole operator: row-statistics pre-pass and the recomputation
  * passes, queued on `stream` (a cudaStream_t) without synchronising.
  * Replaces flash_bwdbwd (fhog/triton_bwdbwd.py:557-648).
  */
