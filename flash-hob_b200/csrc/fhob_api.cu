@@ -31,6 +31,11 @@ __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_
   long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   int lane = threadIdx.x & 31;
+  if (o == nullptr) {
+    // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
+    if (lane == 0) nlc[row] = -lse[row] * kLog2e;
+    return;
+  }
   const T* po = o + row * d;
   const T* pd = d_o + row * d;
   float acc = 0.f;
@@ -54,7 +59,9 @@ __global__ void row_stats_kernel(const float* k1, const float* ndd, const float*
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = true) {
+// `o_optional`: the caller may leave p->o NULL (D is then taken from sum_j P dP inside the sweep
+// that yields dd and b, which only the tensor-core path does)
+int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = true, bool o_optional = false) {
   if (!p) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0) return FHOB_ERR_ARG;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
@@ -63,6 +70,7 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->window < 0 || (p->window > 0 && !p->causal) || p->reserved != 0) return FHOB_ERR_ARG;
   const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->lse, p->ddq, p->ddk, p->ddv};
   for (int i = 0; i < (need_cotangents ? 9 : 6); ++i) {
+    if (i == 3 && !ins[i] && o_optional && p->impl != FHOB_IMPL_SIMT && tc_supported(*p)) continue;
     if (!ins[i]) return FHOB_ERR_ARG;
     if (!aligned16(ins[i])) return FHOB_ERR_ALIGN;
   }
@@ -157,7 +165,7 @@ static int run_prepass(const FhobProblem* p, void* stream) {
 }
 
 int fhob_prepass(const FhobProblem* p, void* stream) {
-  int st = validate(p, false);
+  int st = validate(p, false, true, true);
   if (st != FHOB_OK) return st;
   return run_prepass(p, stream);
 }
@@ -165,10 +173,10 @@ int fhob_prepass(const FhobProblem* p, void* stream) {
 int fhob_pass1(const FhobProblem* p, void* stream) { return run_pass(1, p, stream); }
 int fhob_pass2(const FhobProblem* p, void* stream) { return run_pass(2, p, stream); }
 int fhob_pass12(const FhobProblem* p, void* stream) {
-  int st = validate(p, false);
+  int st = validate(p, false, true, true);
   if (st != FHOB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (use_tc(*p)) return tc_pass(12, *p, s);
+  if (use_tc(*p)) return tc_pass(p->o ? 12 : 13, *p, s);
   st = simt_pass(1, *p, s);
   return st != FHOB_OK ? st : simt_pass(2, *p, s);
 }
@@ -176,14 +184,14 @@ int fhob_pass3(const FhobProblem* p, void* stream) { return run_pass(3, p, strea
 int fhob_pass4(const FhobProblem* p, void* stream) { return run_pass(4, p, stream); }
 
 int fhob_bwdbwd(const FhobProblem* p, void* stream) {
-  int st = validate(p, true);
+  int st = validate(p, true, true, true);
   if (st != FHOB_OK) return st;
-  st = fhob_prepass(p, stream);
+  st = run_prepass(p, stream);
   if (st != FHOB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (use_tc(*p)) {
     // dd and b come out of one sweep (sum_j P dP = D makes b linear in sums that need no dd)
-    static const int kPasses[3] = {12, 3, 4};
+    const int kPasses[3] = {p->o ? 12 : 13, 3, 4};
     for (int pass : kPasses) {
       st = tc_pass(pass, *p, s);
       if (st != FHOB_OK) return st;
@@ -198,7 +206,7 @@ int fhob_bwdbwd(const FhobProblem* p, void* stream) {
 }
 
 int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_out, void* stream) {
-  int st = validate(p, false);
+  int st = validate(p, false, true, true);
   if (st != FHOB_OK) return st;
   RowVectors rv = row_vectors(*p);
   long rows = static_cast<long>(p->bh) * p->n_q;

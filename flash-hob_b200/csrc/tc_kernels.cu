@@ -136,8 +136,9 @@ struct EwCtx {
 
 // FUSED (pass 2 only): accumulates r[0] = sum P A2, r[1] = sum P X, r[2] = sum dP P A2, from which
 // both dd and b follow at the end of the pass without dd being known while the tiles stream by.
-template <int PASS, int BN, bool MASKED, bool FUSED>
-__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float2 (&r)[3]) {
+// FUSED == 2 also accumulates r[3] = sum P dP = D, for callers that do not pass O.
+template <int PASS, int BN, bool MASKED, int FUSED>
+__device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCtx& c, float2 (&r)[4]) {
   float2& rowacc = r[0];
   constexpr int CH = BN / 32;
   const float2 sl2 = make_float2(c.sl2, c.sl2), nlc = make_float2(c.r_nlc, c.r_nlc);
@@ -171,6 +172,7 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
         r[0] = __fadd2_rn(r[0], q);
         r[1] = __ffma2_rn(pr, f2(x[j], x[j + 1]), r[1]);
         r[2] = __ffma2_rn(f2(dp[j], dp[j + 1]), q, r[2]);
+        if (FUSED == 2) r[3] = __ffma2_rn(pr, f2(dp[j], dp[j + 1]), r[3]);
       } else {
         const float2 tt = __ffma2_rn(fa2, scale, ndd);
         float2 u = __ffma2_rn(f2(dp[j], dp[j + 1]), tt, f2(x[j], x[j + 1]));
@@ -274,9 +276,9 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
   tmem_st16(acc + 3 * BN, w_ds2);
 }
 
-template <int PASS, int D, int BN, bool FUSED = false, bool F16 = false>
+template <int PASS, int D, int BN, int FUSED = 0, bool F16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
-  static_assert(!FUSED || PASS == 2, "only pass 2 has a fused form");
+  static_assert(FUSED == 0 || PASS == 2, "only pass 2 has a fused form");
   using C = Cfg<PASS, D, BN>;
   constexpr bool kQStat = PASS != 4;
   // passes 1, 2: a third warp issues the second product of group A (their tensor pipe has the room;
@@ -567,8 +569,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     if (kQStat && g_row < p.n_q) {
       c.r_nlc = p.nlc[vec_head + g_row];
       if (PASS >= 2) {
-        c.r_k1 = p.k1[vec_head + g_row];
-        if (!FUSED) c.r_ndd = p.ndd[vec_head + g_row];
+        if (FUSED != 2) c.r_k1 = p.k1[vec_head + g_row];
+        if (FUSED == 0) c.r_ndd = p.ndd[vec_head + g_row];
       }
       if (PASS >= 3) c.r_k23 = p.k23[vec_head + g_row];
     }
@@ -584,7 +586,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       c.hi = p.n_q - 1;
       if (p.window > 0 && g_row - off + p.window - 1 < c.hi) c.hi = g_row - off + p.window - 1;
     }
-    float2 racc[3] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    float2 racc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     float2& rowacc = racc[0];
     bool ok = true;
     PROF_DECL
@@ -668,11 +670,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (half == 1) bars->red[row] = rb;
       asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (half == 0) rb += bars->red[row];
+      float d_row = -c.r_k1;
+      if (FUSED == 2) {
+        // D = sum P dP (the caller passed no O): it is also what passes 3 and 4 read as k1 = -D
+        d_row = racc[3].x + racc[3].y;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (half == 1) bars->red[row] = d_row;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (half == 0) d_row += bars->red[row];
+      }
       if (half == 0 && ok && g_row < p.n_q) {
-        rb += bars->red[row];
         const float dd = c.scale * r1;
         p.ndd[vec_head + g_row] = -dd;
-        p.k23[vec_head + g_row] = -c.r_k1 * dd - rb;  // -D*dd - b = D*dd - (sum P X + scale * sum dP P A2)
+        p.k23[vec_head + g_row] = d_row * dd - rb;  // -D*dd - b = D*dd - (sum P X + scale * sum dP P A2)
+        if (FUSED == 2) const_cast<float*>(p.k1)[vec_head + g_row] = -d_row;
       }
     } else if (PASS <= 2) {
       if (half == 1) bars->red[row] = rowacc.x + rowacc.y;
@@ -742,7 +754,7 @@ int env_int(const char* name, int dflt) {
   return v ? atoi(v) : dflt;
 }
 
-template <int PASS, int D, int BN, bool FUSED = false, bool F16 = false>
+template <int PASS, int D, int BN, int FUSED = 0, bool F16 = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, D, BN>;
   constexpr auto kernel = tc_pass_kernel<PASS, D, BN, FUSED, F16>;
@@ -798,11 +810,12 @@ template <int D, bool F16>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
   static const int bn1 = env_int("FHOB_TC_BN1", 128);
   switch (pass) {
-    case 1: return bn1 == 64 ? launch<1, D, 64, false, F16>(p, s) : launch<1, D, 128, false, F16>(p, s);
-    case 2: return launch<2, D, 64, false, F16>(p, s);
-    case 12: return launch<2, D, 64, true, F16>(p, s);  // passes 1 and 2 in one sweep
-    case 3: return launch<3, D, 64, false, F16>(p, s);
-    case 4: return launch<4, D, 64, false, F16>(p, s);
+    case 1: return bn1 == 64 ? launch<1, D, 64, 0, F16>(p, s) : launch<1, D, 128, 0, F16>(p, s);
+    case 2: return launch<2, D, 64, 0, F16>(p, s);
+    case 12: return launch<2, D, 64, 1, F16>(p, s);  // passes 1 and 2 in one sweep
+    case 13: return launch<2, D, 64, 2, F16>(p, s);  // the same, also producing D = sum P dP (no O given)
+    case 3: return launch<3, D, 64, 0, F16>(p, s);
+    case 4: return launch<4, D, 64, 0, F16>(p, s);
   }
   return FHOB_ERR_ARG;
 }

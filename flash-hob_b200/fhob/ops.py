@@ -57,6 +57,9 @@ class _Problem:
     def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True,
                  window=None):
         names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
+        no_o = O is None
+        if no_o:
+            O = dO   # stands in for the shape checks; the library gets a NULL pointer
         tensors = [Q, K, V, O, dO, ddQ, ddK, ddV]
         if impl not in _lib.IMPL:
             raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
@@ -100,6 +103,8 @@ class _Problem:
         p.impl = _lib.IMPL[impl]
         p.scale = float(scale)
         p.q, p.k, p.v, p.o, p.d_o = (t.data_ptr() for t in (q, k, v, o, do))
+        if no_o:
+            p.o = None
         p.ddq, p.ddk, p.ddv, p.lse = (t.data_ptr() for t in (ddq, ddk, ddv, lse))
         if need_outputs:
             self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(q)
@@ -137,7 +142,10 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     (fhog/triton_bwdbwd.py:558, :648).  Tensors are ``(BH, N, D)`` like the
     reference or ``(B, H, N, D)``; bfloat16 or float16 (tensor-core kernels,
     fp32 accumulation) or float32 (CUDA-core kernels).  ``L`` is the logsumexp of
-    the masked scaled scores, any float dtype (used as fp32).
+    the masked scaled scores, any float dtype (used as fp32).  ``O`` may be
+    ``None`` for 16-bit inputs on the tensor-core path: ``D = rowsum(dO * O)``
+    (reference :580) is then replaced by the mathematically equal
+    ``sum_j P_ij dP_ij``, which the row-statistics sweep accumulates anyway.
 
     Keyword-only additions, all behaviour-preserving by default:
     ``is_causal`` bottom-right aligned causal mask (the reference operator has
@@ -156,6 +164,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
         return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, sliding_window)
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
+    if O is None:
+        raise ValueError("O=None is only supported for device tensors")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev, window=sliding_window)
 

@@ -73,7 +73,8 @@ typedef struct FhobProblem {
   const void* q;   /* (bh, n_q, d) */
   const void* k;   /* (bh, n_k, d) */
   const void* v;   /* (bh, n_k, d) */
-  const void* o;   /* (bh, n_q, d) forward output */
+  const void* o;   /* (bh, n_q, d) forward output; may be NULL for fhob_bwdbwd / fhob_pass12 on the tensor-core
+                      path: D = rowsum(dO * O) (reference :580) is then replaced by the equal sum_j P dP */
   const void* d_o; /* (bh, n_q, d) cotangent of o in the first backward */
   const void* ddq; /* (bh, n_q, d) cotangent of dQ */
   const void* ddk; /* (bh, n_k, d) cotangent of dK */

@@ -606,3 +606,29 @@ def test_cuda_graph_capture_and_replay():
         assert torch.equal(o_g, o_e) and torch.equal(lse_g, lse_e)
         for g, e in zip(outs, eager):
             assert torch.equal(g, e)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("d", [64, 128])
+def test_bf16_without_saved_output(d, causal):
+    """O=None: D = rowsum(dO * O) is replaced by sum_j P dP, accumulated by the sweep that yields dd
+    and b.  Same results within the bf16 bound, and close to the call that passes O."""
+    import fhob
+    x = make_inputs(2, 384, 512, d, seed=161, dtype=torch.float64)
+    scale = d ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal)
+    lse = O.attn_lse(x["q"], x["k"], scale, causal).float().cuda()
+    o = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal).bfloat16().cuda()
+    dev = {k: v.bfloat16().cuda() for k, v in x.items()}
+    rest = (dev["do"], dev["ddq"], dev["ddk"], dev["ddv"], lse, scale)
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], None, *rest, is_causal=causal, check=True)
+    with_o = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o, *rest, is_causal=causal, check=True)
+    for n, g, w, r in zip(OUT_NAMES, got, with_o, ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
+        assert O.rel_err(g, w.double()) < 1e-2, n
+    stats = fhob.run_passes(dev["q"], dev["k"], dev["v"], None, *rest, is_causal=causal, upto=2, fused12=True)
+    sd, sdd, sb = O.bwdbwd_row_stats(*x.values(), scale, causal)
+    assert O.rel_err(stats["d"], sd) < 5e-3 and O.rel_err(stats["dd"], sdd) < TOL_BF16
+    assert O.rel_err(stats["b"], sb) < TOL_BF16
+    with pytest.raises(RuntimeError, match="invalid argument"):
+        fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], None, *rest, is_causal=causal, impl="simt")
