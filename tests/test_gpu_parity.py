@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN, make_inputs
+from conftest import GOLDEN, ROOT, make_inputs
 from oracle import attn_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -632,3 +632,33 @@ def test_bf16_without_saved_output(d, causal):
     assert O.rel_err(stats["b"], sb) < TOL_BF16
     with pytest.raises(RuntimeError, match="invalid argument"):
         fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], None, *rest, is_causal=causal, impl="simt")
+
+
+@pytest.mark.parametrize("variant", ["FHOB_FORWARD_TWO_SWEEPS"])
+def test_alternative_forward_kernels(variant):
+    """The library's default forward is the single-sweep online-softmax kernel; the two-sweep
+    kernels (log-sum-exp, then P V) stay selectable through the environment and must give the
+    same results.  The choice is read once per process, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import sys, math, torch
+sys.path[:0] = [%r, %r, %r]
+import fhob
+from oracle import attn_oracle as O
+from conftest import make_inputs
+for (bh, nq, nk, d, causal, w) in [(2, 384, 640, 128, False, None), (2, 328, 328, 64, True, None), (1, 512, 700, 128, True, 150)]:
+    x = make_inputs(bh, nq, nk, d, seed=171, dtype=torch.float64)
+    scale = d ** -0.5
+    wl = math.inf if w is None else w
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=wl)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=wl)
+    o, lse = fhob.attention_forward(x["q"].bfloat16().cuda(), x["k"].bfloat16().cuda(), x["v"].bfloat16().cuda(),
+                                    scale, is_causal=causal, sliding_window=w, impl="tcgen05")
+    assert O.rel_err(o, o_ref) < 2e-2 and O.rel_err(lse, l_ref) < 1e-5, (bh, nq, nk, d, causal, w)
+print("ok")
+''' % (str(ROOT), str(ROOT / "flash-hob_b200"), str(ROOT / "tests"))
+    env = dict(os.environ, **{variant: "1"})
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
