@@ -55,7 +55,7 @@ class _Problem:
     """Validated tensors + the FhobProblem struct that points at them."""
 
     def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True,
-                 window=None):
+                 window=None, out=None, workspace=None):
         names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
         no_o = O is None
         if no_o:
@@ -94,7 +94,14 @@ class _Problem:
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         lib = _lib.load()
         nbytes = lib.fhob_workspace_bytes(bh, n_q)
-        self.ws = _workspace(dev, self.stream, nbytes)
+        if workspace is None:
+            self.ws = _workspace(dev, self.stream, nbytes)
+        else:
+            if (workspace.device != dev or workspace.dtype != torch.uint8 or not workspace.is_contiguous()
+                    or workspace.numel() < nbytes or workspace.data_ptr() % 256):
+                raise ValueError(f"workspace: need a contiguous uint8 tensor of at least {nbytes} bytes on {dev}, "
+                                 "256-byte aligned")
+            self.ws = workspace
         p = _lib.FhobProblem()
         p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
         p.dtype = _lib.DTYPES[str(dt)]
@@ -106,7 +113,18 @@ class _Problem:
         if no_o:
             p.o = None
         p.ddq, p.ddk, p.ddv, p.lse = (t.data_ptr() for t in (ddq, ddk, ddv, lse))
-        if need_outputs:
+        if need_outputs and out is not None:
+            want = (q.shape, k.shape, k.shape, q.shape)
+            if len(out) != 4:
+                raise ValueError("out: expected (dQ2, dK2, dV2, ddO)")
+            folded = []
+            for n, t, w_shape in zip(("dQ2", "dK2", "dV2", "ddO"), out, want):
+                if t.device != dev or t.dtype != dt or not t.is_contiguous() or t.numel() != w_shape.numel():
+                    raise ValueError(f"out {n}: need a contiguous {dt} tensor of {tuple(w_shape)} elements on {dev}")
+                folded.append(t.view(w_shape))
+            self.dq2, self.dk2, self.dv2, self.ddo = folded
+            p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
+        elif need_outputs:
             self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(q)
             self.dk2, self.dv2 = torch.empty_like(k), torch.empty_like(k)
             p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
@@ -123,8 +141,10 @@ class _Problem:
         return _lib.load().fhob_read_status(C.byref(self.p), C.c_void_p(self.stream))
 
 
-def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, window=None):
-    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, window=window)
+def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, window=None, out=None,
+                workspace=None):
+    prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, window=window, out=out,
+                    workspace=workspace)
     lib = _lib.load()
     with torch.cuda.device(prob.device):
         _lib.check(lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream)), "fhob_bwdbwd")
@@ -135,7 +155,7 @@ def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check,
 
 def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = False,
                  sliding_window: Optional[int] = None, impl: str = "auto", check: bool = False,
-                 device: Optional[torch.device] = None) -> Tuple[torch.Tensor, ...]:
+                 device: Optional[torch.device] = None, out=None, workspace=None) -> Tuple[torch.Tensor, ...]:
     """Double backward of scaled-dot-product attention.
 
     Same positional signature and return order as the reference
@@ -153,7 +173,10 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     the oracle's ``sliding_window_length`` W (needs ``is_causal``): query i
     then sees only the W keys that end at its causal diagonal; ``impl`` one of
     "auto", "simt", "tcgen05"; ``check`` synchronise and raise if a device
-    wait timed out.
+    wait timed out; ``out`` a tuple ``(dQ2, dK2, dV2, ddO)`` of preallocated
+    contiguous device tensors to write into and ``workspace`` a uint8 device
+    tensor of ``fhob_workspace_bytes`` bytes (the reference allocates both per
+    call, :581-584, :617-618; with them given the call allocates nothing).
 
     Host (CPU) tensors are accepted too: they are staged to ``device``
     (default: current CUDA device) on the current stream, preferably from
@@ -161,11 +184,12 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     a stream synchronise.
     """
     if Q.device.type == "cuda":
-        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, sliding_window)
+        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, sliding_window, out,
+                           workspace)
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
-    if O is None:
-        raise ValueError("O=None is only supported for device tensors")
+    if O is None or out is not None or workspace is not None:
+        raise ValueError("O=None, out= and workspace= are only supported for device tensors")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev, window=sliding_window)
 

@@ -662,3 +662,30 @@ print("ok")
     env = dict(os.environ, **{variant: "1"})
     out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
+
+
+def test_preallocated_outputs_and_workspace():
+    """out= and workspace=: the call writes into the caller's tensors and allocates nothing."""
+    import fhob
+    from fhob import _lib
+    x = make_inputs(3, 256, 320, 128, seed=181, dtype=torch.bfloat16, device="cuda")
+    scale = 128 ** -0.5
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=True)
+    args = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
+    ref = fhob.flash_bwdbwd(*args, is_causal=True, check=True)
+    out = (torch.empty_like(x["q"]), torch.empty_like(x["k"]), torch.empty_like(x["k"]), torch.empty_like(x["q"]))
+    ws = torch.empty(_lib.load().fhob_workspace_bytes(3, 256), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    before = torch.cuda.memory_stats()["allocation.all.allocated"]
+    got = fhob.flash_bwdbwd(*args, is_causal=True, out=out, workspace=ws)
+    after = torch.cuda.memory_stats()["allocation.all.allocated"]
+    torch.cuda.synchronize()
+    assert after == before                      # no tensor was allocated by the call
+    for g, o_t, r in zip(got, out, ref):
+        assert g.data_ptr() == o_t.data_ptr() and torch.equal(g, r)
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, is_causal=True, out=out[:3])
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, is_causal=True, out=(out[0], out[1], out[2], out[3].float()))
+    with pytest.raises(ValueError):
+        fhob.flash_bwdbwd(*args, is_causal=True, workspace=ws[:100])
