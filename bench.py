@@ -54,8 +54,8 @@ EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # workload's shape (N_Q=4096, N_K=8192, D=128), from the ncu capture summarised in
 # profiles/tc_pass_kernels_cfg5_16heads.md (captured with 16 heads; traffic grows in proportion to
 # the heads, every head having its own tensors).  None for shapes that were not captured.
-DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass12"): 190.51e6 / 16,
-                       ("cfg5-shard", "pass3"): 213.07e6 / 16, ("cfg5-shard", "pass4"): 228.74e6 / 16}
+DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass12"): 191.01e6 / 16,
+                       ("cfg5-shard", "pass3"): 207.72e6 / 16, ("cfg5-shard", "pass4"): 229.56e6 / 16}
 KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1, 0>",
                 "pass3": "tc_pass_kernel<3, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0, 0>"}
 
