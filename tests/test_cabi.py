@@ -130,3 +130,18 @@ def test_tile_range_rule_against_the_mask_definition(lib):
                             assert (tb.value, te.value) == (min(want), max(want) + 1)
                     checked += 1
     assert checked > 1000
+
+
+def test_custom_op_is_registered_and_infers_shapes_without_a_gpu():
+    """torch.ops.fhob.bwdbwd exists and its shape-only implementation gives the four result shapes
+    (this is what torch.compile traces; the reference relies on torch.compile, fhog/triton_bwdbwd.py:557)."""
+    import torch
+    import fhob  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        q = torch.empty(2, 3, 128, 64, dtype=torch.bfloat16)
+        k = torch.empty(2, 3, 256, 64, dtype=torch.bfloat16)
+        lse = torch.empty(2, 3, 128)
+        out = torch.ops.fhob.bwdbwd(q, k, k, q, q, q, k, k, lse, 0.125, True, 0)
+    assert [tuple(t.shape) for t in out] == [(2, 3, 128, 64), (2, 3, 256, 64), (2, 3, 256, 64), (2, 3, 128, 64)]
+    assert all(t.dtype == torch.bfloat16 for t in out)

@@ -689,3 +689,27 @@ def test_preallocated_outputs_and_workspace():
         fhob.flash_bwdbwd(*args, is_causal=True, out=(out[0], out[1], out[2], out[3].float()))
     with pytest.raises(ValueError):
         fhob.flash_bwdbwd(*args, is_causal=True, workspace=ws[:100])
+
+
+def test_custom_op_eager_and_compiled():
+    """torch.ops.fhob.bwdbwd equals the Python entry point, and a function that calls it compiles
+    with fullgraph=True (as the reference's entry point is compiled, fhog/triton_bwdbwd.py:557) and
+    reproduces the eager results bit for bit."""
+    import fhob
+    x = make_inputs(2, 256, 384, 128, seed=191, dtype=torch.bfloat16, device="cuda")
+    scale = 128 ** -0.5
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=True)
+    args = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
+    ref = fhob.flash_bwdbwd(*args, is_causal=True, check=True)
+    got = torch.ops.fhob.bwdbwd(*args, True, 0)
+    for g, r in zip(got, ref):
+        assert torch.equal(g, r)
+
+    def step(*a):
+        dq2, dk2, dv2, ddo = torch.ops.fhob.bwdbwd(*a, True, 0)
+        return dq2 + 0, dk2, dv2, ddo
+
+    compiled = torch.compile(step, fullgraph=True, dynamic=False, backend="aot_eager")
+    out = compiled(*args)
+    for g, r in zip(out, ref):
+        assert torch.equal(g, r)
