@@ -26,14 +26,16 @@ namespace {
 template <typename T>
 __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
                                float* __restrict__ nlc, float* __restrict__ k1, int* status, long rows, int d,
-                               float scale) {
+                               int n_q) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
   long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   int lane = threadIdx.x & 31;
+  // the inputs are dense (bh*n_q rows), the row vectors are padded per head
+  const long vrow = (row / n_q) * row_stride(n_q) + row % n_q;
   if (o == nullptr) {
     // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
-    if (lane == 0) nlc[row] = -lse[row] * kLog2e;
+    if (lane == 0) nlc[vrow] = -lse[row] * kLog2e;
     return;
   }
   const T* po = o + row * d;
@@ -43,18 +45,19 @@ __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
-    k1[row] = -acc;
-    nlc[row] = -lse[row] * kLog2e;
+    k1[vrow] = -acc;
+    nlc[vrow] = -lse[row] * kLog2e;
   }
 }
 
 __global__ void row_stats_kernel(const float* k1, const float* ndd, const float* k23, float* d_out, float* dd_out,
-                                 float* b_out, long rows) {
+                                 float* b_out, long rows, int n_q) {
   long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= rows) return;
-  if (d_out) d_out[i] = -k1[i];
-  if (dd_out) dd_out[i] = -ndd[i];
-  if (b_out) b_out[i] = -(k23[i] + k1[i] * ndd[i]);
+  const long v = (i / n_q) * row_stride(n_q) + i % n_q;  // padded per head inside, dense outside
+  if (d_out) d_out[i] = -k1[v];
+  if (dd_out) dd_out[i] = -ndd[v];
+  if (b_out) b_out[i] = -(k23[v] + k1[v] * ndd[v]);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -136,7 +139,7 @@ const char* fhob_last_cuda_error(void) { return g_cuda_error; }
 
 size_t fhob_workspace_bytes(int32_t bh, int32_t n_q) {
   if (bh <= 0 || n_q <= 0) return 0;
-  size_t rows = static_cast<size_t>(bh) * static_cast<size_t>(n_q);
+  size_t rows = static_cast<size_t>(bh) * static_cast<size_t>(row_stride(n_q));
   // the tail pad lets the key-tiled pass read whole 64-query groups of the last head
   return kWorkspaceHeaderBytes + 4 * rows * sizeof(float) + kWorkspaceTailBytes;
 }
@@ -150,15 +153,15 @@ static int run_prepass(const FhobProblem* p, void* stream) {
   if (p->dtype == FHOB_BF16) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
-        rv.status, rows, p->d, p->scale);
+        rv.status, rows, p->d, p->n_q);
   } else if (p->dtype == FHOB_F16) {
     prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
                                                        static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                       rv.status, rows, p->d, p->scale);
+                                                       rv.status, rows, p->d, p->n_q);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                      rv.status, rows, p->d, p->scale);
+                                                      rv.status, rows, p->d, p->n_q);
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
@@ -212,7 +215,7 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
   long rows = static_cast<long>(p->bh) * p->n_q;
   unsigned grid = static_cast<unsigned>((rows + 255) / 256);
   row_stats_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(rv.k1, rv.ndd, rv.k23, d_out, dd_out, b_out,
-                                                                        rows);
+                                                                        rows, p->n_q);
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
 }

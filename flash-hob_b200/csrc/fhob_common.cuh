@@ -38,10 +38,15 @@ struct RowVectors {
   float* k23;   // -D*dd - b
 };
 
+// Entries per head of a row vector: n_q rounded up to a multiple of four, so that every head's
+// slice (and every 64-query group the key-tiled kernels fetch with a bulk copy) starts on a
+// 16-byte boundary whatever n_q is.
+__host__ __device__ inline int row_stride(int n_q) { return (n_q + 3) & ~3; }
+
 inline RowVectors row_vectors(const FhobProblem& p) {
   RowVectors r;
   char* base = static_cast<char*>(p.workspace);
-  size_t n = static_cast<size_t>(p.bh) * static_cast<size_t>(p.n_q);
+  size_t n = static_cast<size_t>(p.bh) * static_cast<size_t>(row_stride(p.n_q));
   r.status = reinterpret_cast<int*>(base);
   float* f = reinterpret_cast<float*>(base + kWorkspaceHeaderBytes);
   r.nlc = f;

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   const int bh = blockIdx.y;
   const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
   const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
-  const size_t voff = static_cast<size_t>(bh) * p.n_q;  // row-vector offset
+  const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);  // row-vector offset
   const int causal_off = p.n_k - p.n_q;
   const int n_stat = kQStationary ? p.n_q : p.n_k;
   const int n_strm = kQStationary ? p.n_k : p.n_q;
@@ -396,7 +396,7 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
   const int m0 = blockIdx.x * TM, bh = blockIdx.y;
   const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
   const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
-  const size_t voff = static_cast<size_t>(bh) * p.n_q;
+  const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);
   const int causal_off = p.n_k - p.n_q;
   const int n_stat = KSIDE ? p.n_k : p.n_q, n_strm = KSIDE ? p.n_q : p.n_k;
   if (KSIDE) {

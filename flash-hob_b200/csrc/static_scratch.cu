@@ -49,7 +49,7 @@ int scratch_for_current_device(void** out) {
 extern "C" int fhob_bwdbwd_static_scratch(const FhobProblem* p, void* stream) {
   if (!p) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0) return FHOB_ERR_ARG;
-  const long long rows = static_cast<long long>(p->bh) * static_cast<long long>(p->n_q);
+  const long long rows = static_cast<long long>(p->bh) * static_cast<long long>(fhob::row_stride(p->n_q));
   if (rows > FHOB_STATIC_SCRATCH_MAX_ROWS) return FHOB_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
   int st = scratch_for_current_device(&scratch);

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             tma_load_3d(dst + i * C::STRM_BYTES + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
                         head);
         if (MODE == FO_BK) {
-          const size_t vo = static_cast<size_t>(head) * p.n_q + n0;
+          const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
           uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
           bulk_load(sv, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
           bulk_load(sv + BN * 4, p.k1 + vo, BN * 4, &bars->strm_full[slot]);
@@ -316,9 +316,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
     const float sl2 = p.scale * kLog2e;
     float r_nlc = 0.f, r_k1 = 0.f;
     if (kQStat && g_row < p.n_q) {
-      const size_t vi = static_cast<size_t>(head) * p.n_q + g_row;
-      if (MODE == FO_FWD) r_nlc = -p.lse[vi] * kLog2e;
+      // L is the caller's dense tensor; the workspace vectors are padded per head
+      if (MODE == FO_FWD) r_nlc = -p.lse[static_cast<size_t>(head) * p.n_q + g_row] * kLog2e;
       if (MODE == FO_BQ) {
+        const size_t vi = static_cast<size_t>(head) * row_stride(p.n_q) + g_row;
         r_nlc = p.nlc[vi];
         r_k1 = p.k1[vi];
       }

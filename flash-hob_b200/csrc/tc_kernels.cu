@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             tma_load_3d(dst + C::strm_base(i) + bx * C::strm_box(i), &p.strm[i], &bars->strm_full[slot], bx * 64,
                         n0, head);
         if (PASS == 4) {
-          const size_t vo = static_cast<size_t>(head) * p.n_q + n0;
+          const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
           uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
           bulk_load(sv + 0 * BN * 4, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
           bulk_load(sv + 1 * BN * 4, p.ndd + vo, BN * 4, &bars->strm_full[slot]);
@@ -605,7 +605,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     const int row = quad * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int g_row = m0 + row;  // stationary row of this thread
-    const size_t vec_head = static_cast<size_t>(head) * p.n_q;
+    const size_t vec_head = static_cast<size_t>(head) * row_stride(p.n_q);
     EwCtx c;
     c.scale = p.scale;
     c.sl2 = p.scale * kLog2e;
@@ -868,7 +868,7 @@ int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
 }  // namespace
 
 bool tc_supported(const FhobProblem& p) {
-  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (p.n_q % 4 == 0);
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128);
 }
 
 int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {

@@ -101,8 +101,9 @@ const char* fhob_last_cuda_error(void);
 
 /*
  * Bytes of scratch one problem needs: a 256-byte header holding the device
- * status word plus four fp32 row vectors of bh*n_q entries (-L*log2e,
- * -D*scale, -dd, -b*scale).  This is the whole extra memory of the operator —
+ * status word plus four fp32 row vectors (-L*log2e, -D, -dd, -D*dd - b) of
+ * bh * ceil4(n_q) entries: each head's slice is padded to a multiple of four
+ * so that it starts on a 16-byte boundary.  This is the whole extra memory of the operator —
  * linear in n_q.  Replaces the reference's D, dD and B temporaries
  * (fhog/triton_bwdbwd.py:580-584).
  */
@@ -223,7 +224,7 @@ int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stre
  * GPU that loads the library until the process exits).  The call performs no
  * cudaMalloc/cudaFree and calls no allocating library routine.
  *
- * Limit: bh * n_q <= FHOB_STATIC_SCRATCH_MAX_ROWS, otherwise
+ * Limit: bh * n_q (n_q rounded up to a multiple of four) <= FHOB_STATIC_SCRATCH_MAX_ROWS, otherwise
  * FHOB_ERR_STATIC_LIMIT is returned and nothing is launched.
  *
  * The first call on each device looks up the device address of that array

@@ -521,7 +521,7 @@ def _random_cases(n, seed):
     cases = []
     while len(cases) < n:
         d = rng.choice([64, 128])
-        nq = 4 * rng.randint(1, 110)             # the tensor-core path needs N_Q % 4 == 0
+        nq = rng.randint(1, 440)                 # any length: the row vectors are padded per head
         nk = rng.randint(1, 450)
         causal = rng.random() < 0.6
         if causal and nk < nq:
@@ -713,3 +713,17 @@ def test_custom_op_eager_and_compiled():
     out = compiled(*args)
     for g, r in zip(out, ref):
         assert torch.equal(g, r)
+
+
+@pytest.mark.parametrize("nq,nk,d,causal", [(1, 300, 64, False), (3, 3, 128, True), (130, 131, 128, True),
+                                            (257, 190, 64, False), (99, 250, 128, True)])
+def test_tensor_core_path_takes_any_query_length(nq, nk, d, causal):
+    """Query lengths that are not multiples of four (or of anything): the per-head row vectors are
+    padded inside the workspace, the tensors themselves are dense."""
+    x = make_inputs(3, nq, nk, d, seed=201, dtype=torch.float64)
+    got, ref, _ = _run(x, d ** -0.5, causal, torch.bfloat16, "tcgen05")
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_BF16, n
+    res, _, (sd, sdd, sb) = _run(x, d ** -0.5, causal, torch.bfloat16, "tcgen05", upto=2, fused12=True)
+    assert O.rel_err(res["d"], sd) < TOL_BF16 and O.rel_err(res["dd"], sdd) < TOL_BF16
+    assert O.rel_err(res["b"], sb) < TOL_BF16
