@@ -727,3 +727,25 @@ def test_tensor_core_path_takes_any_query_length(nq, nk, d, causal):
     res, _, (sd, sdd, sb) = _run(x, d ** -0.5, causal, torch.bfloat16, "tcgen05", upto=2, fused12=True)
     assert O.rel_err(res["d"], sd) < TOL_BF16 and O.rel_err(res["dd"], sdd) < TOL_BF16
     assert O.rel_err(res["b"], sb) < TOL_BF16
+
+
+@pytest.mark.parametrize("bh,nq,nk,d,causal,window", [(3, 217, 273, 128, True, 1), (1, 267, 1, 64, False, None)])
+def test_single_visible_key_gives_vanishing_second_order_terms(bh, nq, nk, d, causal, window):
+    """When every query sees exactly one key the softmax is constant: dQ2, dK2 and dV2 are exactly
+    zero in the oracle and ddO = ddV of that key.  The kernels must return rounding noise only
+    (a relative error is undefined here)."""
+    import fhob
+    import math
+    w = math.inf if window is None else window
+    x = make_inputs(bh, nq, nk, d, seed=211, dtype=torch.float64)
+    x = {k: v.half().double() for k, v in x.items()}
+    scale = d ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal, sliding_window_length=w)
+    dev = {k: v.half().cuda() for k, v in x.items()}
+    kw = dict(is_causal=causal, sliding_window=window, impl="tcgen05")
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **kw)
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o, dev["do"], dev["ddq"], dev["ddk"], dev["ddv"], lse,
+                            scale, check=True, **kw)
+    for n, g, r in zip(OUT_NAMES[:3], got[:3], ref[:3]):
+        assert r.abs().max() < 1e-12 and g.double().abs().max() < 1e-4, n
+    assert O.rel_err(got[3], ref[3]) < 1e-3
