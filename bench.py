@@ -3,22 +3,29 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl fhob|reference]
 
-One "step" is one call of the operator (pre-pass + three sweeps) over one batch
-of synthetic heads resident in HBM.  Work is sharded over batch x heads with no
-collective (weak scaling: every GPU gets the same number of heads), so under
-torchrun each rank runs its own shard and the only communication is the
-barrier/max-reduction around the timed region.  Rank 0 prints ONE JSON line.
+One "step" is one call of the operator (pre-pass + three sweeps) over this
+rank's heads of the job, resident in HBM.  The default job is the multi-GPU
+scaling configuration, bf16 non-causal cross-attention B=16 H=32 N_Q=4096
+N_K=8192 D=128 = 512 heads: one GPU runs all 512, N GPUs run 512/N each
+(strong scaling; heads are independent, so there is no collective on the data
+path - the only communication is the barrier and the max-reduction around the
+timed region).  Rank 0 prints ONE JSON line.  At one GPU the same line also
+carries short runs of the other configurations, the peak-memory sweep over the
+sequence length, a check of the timed outputs against the fp64 oracle, the
+CPU baseline and the reference project's own Triton operator timed on the
+same GPU.
 
 Flop accounting: F_alg = 24*BH*pairs*D (the 12 distinct contractions of the
-maths) is what `value`, `e2e` and `cpu_baseline` use; F_exec = 44*BH*pairs*D
-(22 contractions issued: 5 by the sweep that yields dd and b, 9 by the dQ2/ddO
-pass, 8 by the dK2/dV2 pass) is reported beside it.
+maths) is what `value`, `e2e`, `roofline.achieved` and `cpu_baseline` use;
+F_exec = 44*BH*pairs*D (22 contractions issued: 5 by the sweep that yields dd
+and b, 9 by the dQ2/ddO pass, 8 by the dK2/dV2 pass) is reported beside it.
 """
 from __future__ import annotations
 
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -33,32 +40,31 @@ for _p in (ROOT, ROOT / "flash-hob_b200"):
     if str(_p) not in sys.path:
         sys.path.insert(0, str(_p))
 
-# name -> per-GPU shape.  "cfg5-shard" is 1/8 of the cross-attention scaling configuration
-# (B=16 H=32 -> 512 heads, 64 per GPU), so --gpus 8 is exactly that configuration.
+# name -> the whole job (heads = batch * heads of the configuration)
 WORKLOADS = {
-    "cfg5-shard": dict(bh=64, n_q=4096, n_k=8192, d=128, causal=False, cot=1.0,
-                       desc="bf16 non-causal cross-attention N_Q=4096 N_K=8192 D=128, 64 heads per GPU "
-                            "(B=16 H=32 sharded 8 ways)"),
+    "cfg5": dict(bh=512, n_q=4096, n_k=8192, d=128, causal=False, cot=1.0,
+                 desc="bf16 non-causal cross-attention B=16 H=32 N_Q=4096 N_K=8192 D=128 (512 heads)"),
     "cfg2": dict(bh=64, n_q=2048, n_k=2048, d=64, causal=False, cot=1.0,
                  desc="bf16 non-causal B=4 H=16 N=2048 D=64"),
     "cfg3": dict(bh=128, n_q=4096, n_k=4096, d=128, causal=True, cot=0.1,
                  desc="bf16 causal B=8 H=16 N=4096 D=128, cotangents 0.1*N(0,1)"),
-    "cfg4-shard": dict(bh=4, n_q=32768, n_k=32768, d=128, causal=True, cot=1.0,
-                       desc="bf16 causal N=32768 D=128, 4 heads per GPU (B=1 H=32 sharded 8 ways)"),
+    "cfg4": dict(bh=32, n_q=32768, n_k=32768, d=128, causal=True, cot=1.0,
+                 desc="bf16 causal B=1 H=32 N=32768 D=128"),
     "n8192": dict(bh=32, n_q=8192, n_k=8192, d=128, causal=False, cot=1.0,
                   desc="bf16 non-causal B=1 H=32 N=8192 D=128"),
 }
+# the other configurations carried by the one-GPU line: (workload, heads, steps)
+EXTRAS = (("cfg2", 64, 20), ("cfg3", 128, 8), ("cfg4", 4, 5), ("n8192", 32, 5))
 GEMM_UNITS = {"pass12": 5, "pass3": 9, "pass4": 8}
 EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
-# dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass on the default
-# workload's shape (N_Q=4096, N_K=8192, D=128), from the ncu capture summarised in
-# profiles/tc_pass_kernels_cfg5_16heads.md (captured with 16 heads; traffic grows in proportion to
-# the heads, every head having its own tensors).  None for shapes that were not captured.
-DRAM_BYTES_PER_HEAD = {("cfg5-shard", "pass12"): 191.01e6 / 16,
-                       ("cfg5-shard", "pass3"): 207.72e6 / 16, ("cfg5-shard", "pass4"): 229.56e6 / 16}
+# dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass at N_Q=4096,
+# N_K=8192, D=128, from an ncu capture of a 16-head case (every head has its own tensors, so the
+# traffic of a launch grows in proportion to its heads).
+DRAM_BYTES_PER_HEAD = {("cfg5", "pass12"): 191.01e6 / 16, ("cfg5", "pass3"): 207.72e6 / 16,
+                       ("cfg5", "pass4"): 229.56e6 / 16}
 KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1, 0>",
                 "pass3": "tc_pass_kernel<3, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0, 0>"}
-
+METRIC = "double_backward_attention_tflops"
 
 _JSON_FD = None
 
@@ -158,13 +164,12 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(clocks), samples_total=total)
 
 
-def make_batch(w, device, seed):
+def make_batch(w, heads, device, seed):
     g = torch.Generator(device=device).manual_seed(seed)
     def rnd(n, s=1.0):
-        return (torch.randn(w["bh"], n, w["d"], generator=g, device=device, dtype=torch.float32) * s).bfloat16()
-    x = dict(q=rnd(w["n_q"]), k=rnd(w["n_k"]), v=rnd(w["n_k"]), do=rnd(w["n_q"], w["cot"]),
-             ddq=rnd(w["n_q"], w["cot"]), ddk=rnd(w["n_k"], w["cot"]), ddv=rnd(w["n_k"], w["cot"]))
-    return x
+        return (torch.randn(heads, n, w["d"], generator=g, device=device, dtype=torch.float32) * s).bfloat16()
+    return dict(q=rnd(w["n_q"]), k=rnd(w["n_k"]), v=rnd(w["n_k"]), do=rnd(w["n_q"], w["cot"]),
+                ddq=rnd(w["n_q"], w["cot"]), ddk=rnd(w["n_k"], w["cot"]), ddv=rnd(w["n_k"], w["cot"]))
 
 
 def cpu_reference_sample(w, reps, warmup):
@@ -188,37 +193,144 @@ def cpu_reference_sample(w, reps, warmup):
                        f"{reps} steps after {warmup} warm-up, median {sec*1e3:.0f} ms)"), sec
 
 
+def config_block(name, w, heads, world):
+    return dict(workload=name, description=w["desc"], heads=w["bh"], heads_per_gpu=heads, n_q=w["n_q"], n_k=w["n_k"],
+                d=w["d"], causal=w["causal"],
+                parallelism=f"batch*heads split over {world} GPU(s) (strong scaling), no collective")
+
+
 def run_reference(args, w, rank):
+    """The reference arm: the reference's CPU path.  Its own double backward is JAX/XLA, which is
+    not installed (and cannot be, offline), so the arm times the oracle's restatement of
+    jax.vjp(attn_bwd) on all host cores, one head of the workload per step."""
     if rank != 0:
         return
     reps = max(1, args.steps)
-    cb, sec = cpu_reference_sample(w, reps, max(1, min(args.warmup, 2)))
-    line = dict(metric="double_backward_attention_tflops", value=cb["value"], unit="TFLOP/s", impl="reference",
-                n_gpus=args.gpus, steps=reps, warmup=max(1, min(args.warmup, 2)), ms_per_step=sec * 1e3,
-                higher_is_better=True, scaling="weak", vs_baseline=None, dtype="f32", data="synthetic",
-                config=dict(workload=args.workload, description=w["desc"], bh_per_gpu=w["bh"], n_q=w["n_q"],
-                            n_k=w["n_k"], d=w["d"], causal=w["causal"],
-                            sample="each step is a bounded sample of the workload: 1 head on the host CPU"),
-                cpu_baseline=cb,
-                e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
-                note="reference XLA double-backward cannot run (jax is not installed); this is the CPU oracle "
-                     "port of jax.vjp(attn_bwd) on the box's host cores")
-    emit(line)
+    warm = max(1, min(args.warmup, 2))
+    cb, sec = cpu_reference_sample(w, reps, warm)
+    cfg = config_block(args.workload, w, w["bh"] // max(1, args.gpus), args.gpus)
+    cfg["sample"] = "each step is a bounded sample of the workload: 1 head on the host CPU"
+    emit(dict(metric=METRIC, value=cb["value"], unit="TFLOP/s", impl="reference", n_gpus=args.gpus, steps=reps,
+              warmup=warm, ms_per_step=sec * 1e3, higher_is_better=True, scaling="strong", vs_baseline=None,
+              dtype="f32", data="synthetic", config=cfg, cpu_baseline=cb,
+              e2e=dict(value=cb["value"], unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+              note="reference XLA double-backward cannot run (jax is not installed); this is the CPU oracle "
+                   "port of jax.vjp(attn_bwd) on the box's host cores"))
 
 
-def mem_sweep():
-    """Peak memory of one operator call against sequence length (bf16 causal, 2 heads, D=128).
+class Case:
+    """One workload resident on one GPU: inputs, saved forward results, the operator call."""
 
-    Prints one JSON line: per length the bytes of the nine inputs, of the four outputs, the extra
-    bytes the call allocated beyond its outputs (the workspace) and what a dense fp32 score
-    matrix per head pair would have taken."""
+    def __init__(self, w, heads, dev, seed):
+        import fhob
+        self.w, self.heads, self.dev = w, heads, dev
+        self.x = make_batch(w, heads, dev, seed)
+        self.scale = w["d"] ** -0.5
+        x = self.x
+        self.o, self.lse = fhob.attention_forward(x["q"], x["k"], x["v"], self.scale, is_causal=w["causal"])
+        self.args = (x["q"], x["k"], x["v"], self.o, x["do"], x["ddq"], x["ddk"], x["ddv"], self.lse, self.scale)
+        self.in_bytes = sum(t.numel() * t.element_size() for t in self.args[:9])
+        self.out_bytes = 2 * (x["q"].numel() + x["k"].numel()) * 2
+        self.unit_flops = 2.0 * heads * pairs(w) * w["d"]
+
+    def step(self):
+        import fhob
+        return fhob.flash_bwdbwd(*self.args, is_causal=self.w["causal"])
+
+    def status(self):
+        from fhob.ops import _Problem
+        return _Problem(*self.args, self.w["causal"], "auto").status()
+
+    def time_passes(self, iters):
+        """Average CUDA-event time of each stage over `iters` runs of the four stages (after two untimed)."""
+        from fhob import _lib
+        from fhob.ops import _Problem
+        prob = _Problem(*self.args, self.w["causal"], "auto")
+        lib = _lib.load()
+        stages = ["prepass", "pass12", "pass3", "pass4"]
+        acc = {s: 0.0 for s in stages}
+        s_ptr = C.c_void_p(prob.stream)
+        recorded = []
+        for it in range(2 + iters):
+            evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
+            evs[0].record()
+            for i, s in enumerate(stages):
+                _lib.check(getattr(lib, f"fhob_{s}")(C.byref(prob.p), s_ptr), s)
+                evs[i + 1].record()
+            if it % 8 == 7:
+                torch.cuda.synchronize()   # keeps the launch queue short
+            if it >= 2:
+                recorded.append(evs)
+        torch.cuda.synchronize()
+        for evs in recorded:
+            for i, s in enumerate(stages):
+                acc[s] += evs[i].elapsed_time(evs[i + 1])
+        peaks = measured_peaks()
+        out = {}
+        for s in stages:
+            ms = acc[s] / iters
+            out[s] = dict(ms=round(ms, 4))
+            if s in GEMM_UNITS:
+                tf = GEMM_UNITS[s] * self.unit_flops / (ms * 1e-3) / 1e12
+                out[s].update(contractions=GEMM_UNITS[s], tflops_exec=round(tf, 1),
+                              frac_of_sustained_peak=round(tf / peaks["sustained"], 4),
+                              frac_of_burst_peak=round(tf / peaks["burst"], 4))
+        return out
+
+    def check_head(self, outs, head):
+        """Max relative error of one head of `outs` against the chunked fp64 oracle (run on the GPU)."""
+        from oracle import attn_oracle as O
+        x = self.x
+        ref = O.bwdbwd_closed_form_chunked(*(x[n][head].double() for n in ("q", "k", "v", "do", "ddq", "ddk", "ddv")),
+                                           self.scale, self.w["causal"], chunk=1024)
+        return {n: O.rel_err(g[head], r) for n, g, r in zip(("dq2", "dk2", "dv2", "ddo"), outs, ref[:4])}
+
+
+def summarise(w, heads, ms_step, world=1):
+    """value and fractions of the measured cuBLAS bf16 peaks for `world` ranks of `heads` heads each."""
+    peaks = measured_peaks()
+    per_gpu = f_alg(w, heads) / (ms_step * 1e-3) / 1e12
+    return dict(tflops_alg=per_gpu, tflops_exec=per_gpu * EXEC_OVER_ALG,
+                frac_bf16_burst_alg=per_gpu / peaks["burst"], frac_bf16_sustained_alg=per_gpu / peaks["sustained"],
+                frac_bf16_burst_exec=per_gpu * EXEC_OVER_ALG / peaks["burst"],
+                frac_bf16_sustained_exec=per_gpu * EXEC_OVER_ALG / peaks["sustained"])
+
+
+def run_extra(name, heads, steps, dev):
+    """A short device-resident run of another configuration (one GPU): warm-up, `steps` timed
+    steps, per-pass times, one head checked against the oracle."""
+    w = dict(WORKLOADS[name])
+    case = Case(w, heads, dev, seed=4321)
+    for _ in range(3):
+        outs = case.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        outs = case.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    status = case.status()
+    res = dict(description=w["desc"], heads=heads, steps=steps, ms_per_step=round(ms, 4), device_status=status,
+               inputs_mb=round(case.in_bytes / 1e6, 1))
+    res.update({k: round(v, 4) for k, v in summarise(w, heads, ms).items()})
+    res["passes"] = case.time_passes(max(3, steps // 2))
+    res["max_rel_err_vs_fp64_oracle"] = case.check_head(outs, heads - 1)
+    return res
+
+
+def mem_sweep(dev):
+    """Peak memory of one operator call against sequence length (bf16 causal, 2 heads, D=128): per
+    length the bytes of the nine inputs, of the four outputs, the extra bytes the call allocated
+    beyond its outputs (the workspace, 1 MiB minimum block) and what dense fp32 score matrices
+    would have taken."""
     import fhob
     from fhob import ops
-    dev = torch.device("cuda", 0)
     rows = []
     for n in (2048, 4096, 8192, 16384, 32768, 65536):
         w = dict(bh=2, n_q=n, n_k=n, d=128, causal=True, cot=1.0)
-        x = make_batch(w, dev, 7)
+        x = make_batch(w, 2, dev, 7)
         o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 128 ** -0.5, is_causal=True)
         torch.cuda.synchronize()
         ops._workspaces.clear()
@@ -233,28 +345,120 @@ def mem_sweep():
         rows.append(dict(n=n, input_bytes=in_bytes, output_bytes=out_bytes, extra_bytes=peak - out_bytes,
                          dense_fp32_scores_bytes=2 * n * n * 4))
         del x, o, lse, outs
-    print(json.dumps(dict(mem_sweep=rows, note="extra_bytes = workspace (status word + 4 fp32 row vectors, "
-                          "1 MiB minimum block); grows linearly with n")), flush=True)
+    ops._workspaces.clear()
+    torch.cuda.empty_cache()
+    return rows
 
+
+# ---------------------------------------------------------------- the reference's Triton operator
+
+def competitor_child(args):
+    """Times the reference project's own operator (fhog.flash_bwdbwd, Triton, installed unmodified
+    under baseline/_ref) on this GPU and compares its results with this library's.  Prints one
+    JSON object.  Non-causal shapes with lengths that are multiples of its tiles only: it has no
+    causal mask and no bounds checks."""
+    ref_dir = ROOT / "baseline" / "_ref"
+    if not (ref_dir / "fhog" / "triton_bwdbwd.py").exists():
+        print(json.dumps(dict(error=f"{ref_dir.relative_to(ROOT)} is missing (baseline/install_reference.sh "
+                                    "installs the reference there)")))
+        return
+    cache = ROOT / "baseline" / "_triton_cache"
+    if cache.is_dir():
+        os.environ.setdefault("TRITON_CACHE_DIR", str(cache))
+    sys.path.insert(0, str(ref_dir))
+    import fhob
+    from oracle import attn_oracle as O
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    w = dict(WORKLOADS[args.workload])
+    heads = args.heads or w["bh"]
+    assert not w["causal"]
+    case = Case(w, heads, dev, seed=777)
+    t0 = time.time()
+    from fhog.triton_bwdbwd import bwdbwd_kernel_stage1, bwdbwd_kernel_stage2, flash_bwdbwd as ref_bwdbwd
+    theirs = ref_bwdbwd(*case.args)          # first call: torch.compile + Triton autotune over its config list
+    torch.cuda.synchronize()
+    setup_s = time.time() - t0
+    for _ in range(2):
+        theirs = ref_bwdbwd(*case.args)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        theirs = ref_bwdbwd(*case.args)
+    e1.record()
+    torch.cuda.synchronize()
+    ms_ref = e0.elapsed_time(e1) / args.steps
+    for _ in range(3):
+        ours = case.step()
+    e0.record()
+    for _ in range(args.steps):
+        ours = case.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_ours = e0.elapsed_time(e1) / args.steps
+    def cfg(k):
+        b = getattr(k, "best_config", None)
+        return str(b) if b is not None else None
+    names = ("dq2", "dk2", "dv2", "ddo")
+    oracle_err_theirs = case.check_head(theirs, heads - 1)
+    oracle_err_ours = case.check_head(ours, heads - 1)
+    print(json.dumps(dict(
+        workload=args.workload, heads=heads, steps=args.steps, setup_s=round(setup_s, 1),
+        reference_triton=dict(ms_per_step=round(ms_ref, 4), tflops_alg=round(f_alg(w, heads) / ms_ref / 1e9, 1),
+                              autotuned_stage1=cfg(bwdbwd_kernel_stage1), autotuned_stage2=cfg(bwdbwd_kernel_stage2),
+                              max_rel_err_vs_fp64_oracle=oracle_err_theirs),
+        this_library=dict(ms_per_step=round(ms_ours, 4), tflops_alg=round(f_alg(w, heads) / ms_ours / 1e9, 1),
+                          max_rel_err_vs_fp64_oracle=oracle_err_ours),
+        speedup=round(ms_ref / ms_ours, 2),
+        max_rel_diff_between_the_two={n: O.rel_err(a, b.float()) for n, a, b in zip(names, ours, theirs)})))
+
+
+def competitor_triton(cases, steps, timeout_s):
+    """Runs `competitor_child` once per (workload, heads) in a child process with a time limit, so
+    that a slow autotune or a failure of the reference's code cannot take the benchmark line down."""
+    out = {}
+    for name, heads in cases:
+        cmd = [sys.executable, str(ROOT / "bench.py"), "--competitor-child", "--workload", name, "--heads", str(heads),
+               "--steps", str(steps)]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+            lines = [l for l in r.stdout.strip().splitlines() if l.startswith("{")]
+            out[name] = json.loads(lines[-1]) if lines else dict(
+                error=f"exit code {r.returncode}: " + (r.stderr.strip().splitlines() or ["no output"])[-1][:300])
+        except subprocess.TimeoutExpired:
+            out[name] = dict(error=f"no result within {timeout_s} s (Triton compiles and times every configuration "
+                                   "of the reference's autotune list on the first call)")
+        except Exception as e:  # noqa: BLE001
+            out[name] = dict(error=f"{type(e).__name__}: {e}"[:300])
+    return out
+
+
+# ---------------------------------------------------------------- main
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="cfg5-shard", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
+    ap.add_argument("--heads", type=int, default=0, help="heads of the whole job (default: the workload's); "
+                    "smaller values give the small cases profiler captures need")
+    ap.add_argument("--min-timed-s", type=float, default=1.0,
+                    help="rounds of --steps steps are repeated until at least this much device time is covered")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-producers", action="store_true", help="do not time the forward / first-backward kernels")
     ap.add_argument("--no-clocks", action="store_true", help="do not sample clocks with nvidia-smi")
-    ap.add_argument("--heads", type=int, default=0, help="heads per GPU (default: the workload's); "
-                    "smaller values give the small cases profiler captures need")
-    ap.add_argument("--mem-sweep", action="store_true",
-                    help="instead of the benchmark: peak device memory of one call vs sequence length")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="one GPU: skip the other configurations, the memory sweep and the Triton comparison")
+    ap.add_argument("--no-competitor", action="store_true", help="skip only the reference's Triton operator")
+    ap.add_argument("--competitor-timeout", type=int, default=300)
+    ap.add_argument("--competitor-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
-    if args.mem_sweep:
-        mem_sweep()
+    if args.competitor_child:
+        competitor_child(args)
         return
     claim_stdout()
     w = dict(WORKLOADS[args.workload])
@@ -270,8 +474,8 @@ def main():
 
     import torch.distributed as dist
     import fhob
-    from fhob import _lib
-    from fhob.ops import _Problem
+    from fhob.hostmem import near_device
+    from fhob.sharding import head_shard, max_over_ranks as _max_over_ranks
 
     warmup = max(3, args.warmup)
     torch.cuda.set_device(local)
@@ -284,23 +488,14 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    from fhob.sharding import head_shard, max_over_ranks as _max_over_ranks
-
     def max_over_ranks(ms):
         return _max_over_ranks(ms, device=dev)
 
-    # weak scaling: the job has bh*world heads and every rank owns a contiguous shard of bh of them
-    shard_start, shard_heads = head_shard(w["bh"] * world, world, rank)
-    assert shard_heads == w["bh"]
-    x = make_batch(w, dev, 1234 + shard_start)
-    scale = w["d"] ** -0.5
-    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=w["causal"])
-    args_dev = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
-    in_bytes = sum(t.numel() * t.element_size() for t in args_dev[:9])
-    out_bytes = 2 * (x["q"].numel() + x["k"].numel()) * 2
-
-    def step():
-        return fhob.flash_bwdbwd(*args_dev, is_causal=w["causal"])
+    # strong scaling: the job's heads are split into contiguous shards, one per rank
+    shard_start, shard_heads = head_shard(w["bh"], world, rank)
+    if shard_heads == 0:
+        raise SystemExit(f"rank {rank}: the job has fewer heads ({w['bh']}) than ranks ({world})")
+    case = Case(w, shard_heads, dev, seed=1234 + shard_start)
 
     # ---- device-resident timing
     sampler = ClockSampler(local) if rank == 0 and not args.no_clocks else None
@@ -313,68 +508,75 @@ def main():
     done_w = 0
     outs = None
     while done_w < warmup or time.time() - t_w < 0.3:
-        outs = step()   # same allocation pattern as the timed loop: no cudaMalloc is left for it
+        outs = case.step()   # same allocation pattern as the timed loop: no cudaMalloc is left for it
         done_w += 1
         if done_w % 4 == 0:
             torch.cuda.synchronize()
+    torch.cuda.synchronize()
     warmup = done_w
+    est_ms = (time.time() - t_w) * 1e3 / done_w
+    # rounds of exactly `steps` steps; enough of them to cover --min-timed-s of device time
+    rounds = max(1, min(50, math.ceil(args.min_timed_s * 1e3 / max(est_ms * args.steps, 1e-3))))
+    if world > 1:
+        t = torch.tensor([rounds], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rounds = int(t.item())
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    round_ms = []
     t_start = time.time()
-    e0.record()
-    for _ in range(args.steps):
-        outs = step()
-    e1.record()
-    barrier()
+    for _ in range(rounds):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            outs = case.step()
+        e1.record()
+        barrier()
+        round_ms.append(max_over_ranks(e0.elapsed_time(e1)))
     t_end = time.time()
-    ms_total = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.window(t_start, t_end) if sampler else None
-    ms_step = ms_total / args.steps
-    prob = _Problem(*args_dev, w["causal"], "auto")
-    status = prob.status()
+    ms_step = statistics.median(round_ms) / args.steps
+    status = case.status()
     if status != 0:
         raise RuntimeError(f"device status {status} after the timed region")
 
+    # ---- the timed outputs against the fp64 oracle (one head, outside the timed region)
+    parity = case.check_head(outs, shard_heads - 1) if rank == 0 else None
+
     # ---- per-pass timing (same stream, CUDA events between the stages)
-    lib = _lib.load()
-    stages = ["prepass", "pass12", "pass3", "pass4"]
-    acc = {s: 0.0 for s in stages}
-    s_ptr = C.c_void_p(prob.stream)
-    for it in range(2 + args.steps):
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(len(stages) + 1)]
-        evs[0].record()
-        for i, s in enumerate(stages):
-            _lib.check(getattr(lib, f"fhob_{s}")(C.byref(prob.p), s_ptr), s)
-            evs[i + 1].record()
-        torch.cuda.synchronize()
-        if it >= 2:
-            for i, s in enumerate(stages):
-                acc[s] += evs[i].elapsed_time(evs[i + 1])
     peaks = measured_peaks()
-    unit_flops = 2.0 * w["bh"] * pairs(w) * w["d"]
-    passes = {}
-    for s in stages:
-        ms = acc[s] / args.steps
-        passes[s] = dict(ms=round(ms, 4))
-        if s in GEMM_UNITS:
-            tf = GEMM_UNITS[s] * unit_flops / (ms * 1e-3) / 1e12
-            passes[s].update(tflops=round(tf, 1), frac_of_sustained_peak=round(tf / peaks["sustained"], 4))
+    passes = case.time_passes(max(args.steps, 10) * (2 if est_ms < 30 else 1))
     dom = max(GEMM_UNITS, key=lambda s: passes[s]["ms"])
-    per_head = DRAM_BYTES_PER_HEAD.get((args.workload, dom))
     for s in GEMM_UNITS:
         ph = DRAM_BYTES_PER_HEAD.get((args.workload, s))
-        passes[s]["dram_traffic_bytes"] = ph * w["bh"] if ph else None
-    roofline = dict(bound="tensor", kernel=KERNEL_NAMES[dom].format(d=w["d"]), achieved=passes[dom]["tflops"],
-                    peak=peaks["sustained"], unit="TFLOP/s",
-                    frac=round(passes[dom]["tflops"] / peaks["sustained"], 4),
-                    frac_of_burst_peak=round(passes[dom]["tflops"] / peaks["burst"], 4),
-                    peak_source=f"{peaks['src']} cuBLAS bf16 (sustained, kernel timed inside a long step)",
-                    flops_basis=f"{GEMM_UNITS[dom]} contractions of 2*BH*pairs*D flop issued by this pass",
-                    traffic=per_head * w["bh"] if per_head else None)
+        passes[s]["dram_traffic_bytes"] = ph * shard_heads if ph else None
+        passes[s]["share_of_step"] = round(passes[s]["ms"] / sum(passes[k]["ms"] for k in passes), 4)
+    per_head = DRAM_BYTES_PER_HEAD.get((args.workload, dom))
+    per_gpu = summarise(w, shard_heads, ms_step)
+    roofline = dict(
+        bound="tensor", unit="TFLOP/s",
+        achieved=round(per_gpu["tflops_alg"], 1), peak=peaks["sustained"], frac=round(per_gpu["frac_bf16_sustained_alg"], 4),
+        basis="whole operator on one GPU, algorithmic flops (12 contractions: F_alg = 24*BH*pairs*D) / step time; "
+              "the operator issues 22 contractions (recomputation in three sweeps), so 12/22 = 0.545 is the "
+              "ceiling of this figure",
+        frac_of_burst_peak=round(per_gpu["frac_bf16_burst_alg"], 4), peak_burst=peaks["burst"],
+        peak_source=f"{peaks['src']} cuBLAS bf16: sustained (seconds-long loop under the power cap; the timed "
+                    f"region here is {sum(round_ms) / 1e3:.1f} s) and burst",
+        executed=dict(achieved=round(per_gpu["tflops_exec"], 1), frac=round(per_gpu["frac_bf16_sustained_exec"], 4),
+                      frac_of_burst_peak=round(per_gpu["frac_bf16_burst_exec"], 4),
+                      basis="the same with the 22 issued contractions (what the tensor pipe executes)"),
+        dominant_kernel=dict(kernel=KERNEL_NAMES[dom].format(d=w["d"]), ms=passes[dom]["ms"],
+                             share_of_step=passes[dom]["share_of_step"], achieved_exec=passes[dom]["tflops_exec"],
+                             frac_exec=passes[dom]["frac_of_sustained_peak"],
+                             frac_exec_of_burst_peak=passes[dom]["frac_of_burst_peak"],
+                             basis=f"{GEMM_UNITS[dom]} contractions of 2*BH*pairs*D flop issued by this launch / its "
+                                   "average CUDA-event time"),
+        traffic=per_head * shard_heads if per_head else None,
+        traffic_note="dominant kernel, per launch: ncu dram bytes of a 16-head capture scaled by the heads")
 
     # ---- the producers either side of the operator (forward: O and L; first backward: dQ, dK, dV),
     # outside the timed region; algorithmic counts: 2 and 5 contractions of 2*BH*pairs*D flop
     producers = None
+    x = case.x
     if not args.no_producers:
         from fhob.autograd import attention_backward
         def timed(fn, reps=5):
@@ -386,58 +588,110 @@ def main():
             e1.record()
             torch.cuda.synchronize()
             return e0.elapsed_time(e1) / reps
-        ms_f = timed(lambda: fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=w["causal"]))
-        ms_b = timed(lambda: attention_backward(x["q"], x["k"], x["v"], o, x["do"], lse, scale,
+        ms_f = timed(lambda: fhob.attention_forward(x["q"], x["k"], x["v"], case.scale, is_causal=w["causal"]))
+        ms_b = timed(lambda: attention_backward(x["q"], x["k"], x["v"], case.o, x["do"], case.lse, case.scale,
                                                 is_causal=w["causal"]))
         producers = dict(
-            forward=dict(ms=round(ms_f, 4), tflops_alg=round(2 * unit_flops / (ms_f * 1e-3) / 1e12, 1),
+            forward=dict(ms=round(ms_f, 4), tflops_alg=round(2 * case.unit_flops / (ms_f * 1e-3) / 1e12, 1),
                          executed_contractions=2, kernels="fo_kernel<4,..> (single sweep, online softmax)"),
-            first_backward=dict(ms=round(ms_b, 4), tflops_alg=round(5 * unit_flops / (ms_b * 1e-3) / 1e12, 1),
+            first_backward=dict(ms=round(ms_b, 4), tflops_alg=round(5 * case.unit_flops / (ms_b * 1e-3) / 1e12, 1),
                                 executed_contractions=7, kernels="prepass + fo_kernel<2,..> (dQ) + fo_kernel<3,..> (dK, dV)"))
 
     # ---- end to end through the public entry point with host buffers
     e2e = None
     if not args.no_e2e:
-        host = [t.cpu().pin_memory() for t in args_dev[:9]]
+        with near_device(dev) as placement:
+            host = [t.cpu().pin_memory() for t in case.args[:9]]
+            host_out = tuple(torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+                             for t in (x["q"], x["k"], x["k"], x["q"]))
+        # what the link gives one direction at a time (pinned memory, one large copy each way)
+        big = max(host[:8], key=lambda t: t.numel())
+        dst = torch.empty_like(big, device=dev)
+        link = {}
+        for name, fn in (("h2d", lambda: dst.copy_(big, non_blocking=True)),
+                         ("d2h", lambda: host_out[1].copy_(x["k"], non_blocking=True))):
+            fn()
+            torch.cuda.synchronize()
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            nbytes = (big if name == "h2d" else x["k"]).numel() * 2
+            link[name] = nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+        del dst
+        def e2e_step():
+            return fhob.flash_bwdbwd(*host, case.scale, is_causal=w["causal"], device=dev, out=host_out)
         for _ in range(2):
-            fhob.flash_bwdbwd(*host, scale, is_causal=w["causal"], device=dev)
+            e2e_step()
         barrier()
         n_e2e = max(2, min(args.steps, 5))
         e0.record()
         for _ in range(n_e2e):
-            fhob.flash_bwdbwd(*host, scale, is_causal=w["causal"], device=dev)
+            e2e_step()
         e1.record()
         barrier()
         ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
-        e2e = dict(value=f_alg(w) * world / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms_e2e,
-                   h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes, steps=n_e2e)
+        e2e = dict(value=f_alg(w) / (ms_e2e * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=ms_e2e,
+                   h2d_bytes_per_step=case.in_bytes, d2h_bytes_per_step=case.out_bytes, steps=n_e2e,
+                   note="bytes are this rank's (rank 0); inputs in pinned host memory, results into pinned host "
+                        "tensors passed as out=, uploads, kernels and downloads of head ranges overlapped",
+                   h2d_gbs=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9, 1),
+                   d2h_gbs=round(case.out_bytes / (ms_e2e * 1e-3) / 1e9, 1),
+                   link_alone_h2d_gbs=round(link["h2d"], 1), link_alone_d2h_gbs=round(link["d2h"], 1),
+                   frac_of_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d"], 3),
+                   host_placement=placement)
+        del host, host_out
 
+    peak_mem = torch.cuda.max_memory_allocated(dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    cpu_baseline = None
-    if world == 1 and not args.no_cpu_baseline:
-        cpu_baseline, _ = cpu_reference_sample(w, reps=3, warmup=1)
 
-    value = f_alg(w) * world / (ms_step * 1e-3) / 1e12
+    # ---- one GPU only: the other configurations, memory against sequence length, the
+    # reference's Triton operator on the same GPU, the CPU baseline
+    extras = sweep = competitor = cpu_baseline = None
+    if world == 1:
+        del case, outs, x
+        torch.cuda.empty_cache()
+        if not args.no_extras:
+            extras = {}
+            for name, heads, steps in EXTRAS:
+                key = name if heads == WORKLOADS[name]["bh"] else f"{name}-shard"
+                try:
+                    extras[key] = run_extra(name, heads, steps, dev)
+                except Exception as e:  # noqa: BLE001
+                    extras[key] = dict(error=f"{type(e).__name__}: {e}"[:300])
+                torch.cuda.empty_cache()
+            sweep = mem_sweep(dev)
+            if not args.no_competitor:
+                torch.cuda.empty_cache()
+                competitor = competitor_triton((("cfg2", 64), ("cfg5", 16)), steps=10, timeout_s=args.competitor_timeout)
+        if not args.no_cpu_baseline:
+            cpu_baseline, _ = cpu_reference_sample(w, reps=3, warmup=1)
+
+    value = f_alg(w) / (ms_step * 1e-3) / 1e12
+    cfg = config_block(args.workload, w, shard_heads, world)
+    cfg["l2"] = "inputs larger than L2: %.0f MB read per step and GPU" % (case_in_mb(w, shard_heads))
     line = dict(
-        metric="double_backward_attention_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps,
-        warmup=warmup, ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16",
-        data="synthetic",
-        config=dict(workload=args.workload, description=w["desc"], bh_per_gpu=w["bh"], n_q=w["n_q"], n_k=w["n_k"],
-                    d=w["d"], causal=w["causal"], parallelism=f"batch*heads sharded over {world} GPU(s), no collective",
-                    l2="inputs larger than L2: %.0f MB read per step" % (in_bytes / 1e6)),
-        per_gpu=dict(tflops_alg=value / world, tflops_exec=value / world * EXEC_OVER_ALG,
-                     frac_bf16_peak_alg=value / world / peaks["burst"],
-                     frac_bf16_peak_exec=value / world * EXEC_OVER_ALG / peaks["burst"],
-                     frac_bf16_sustained_exec=value / world * EXEC_OVER_ALG / peaks["sustained"]),
-        flops=dict(f_alg_per_step=f_alg(w) * world, f_exec_per_step=f_alg(w) * world * EXEC_OVER_ALG),
-        passes=passes, roofline=roofline, producers=producers, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
-        gpu_launches=4 * args.steps, peak_mem_bytes=torch.cuda.max_memory_allocated(dev))
+        metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=warmup,
+        rounds=rounds, ms_per_step=ms_step, ms_per_round=[round(m, 3) for m in round_ms],
+        timing="median over `rounds` rounds of exactly `steps` steps each (CUDA events, max over ranks per round)",
+        higher_is_better=True, scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic", config=cfg,
+        per_gpu=per_gpu, flops=dict(f_alg_per_step=f_alg(w), f_exec_per_step=f_alg(w) * EXEC_OVER_ALG),
+        passes=passes, roofline=roofline, parity_of_timed_outputs=dict(
+            max_rel_err_vs_fp64_oracle=parity, head="last head of rank 0's shard", tolerance=2e-2),
+        producers=producers, cpu_baseline=cpu_baseline, e2e=e2e, clocks=clocks,
+        gpu_launches=4 * args.steps * rounds, peak_mem_bytes=peak_mem,
+        other_configs=extras, mem_sweep=sweep, competitor_triton=competitor)
     emit(line)
     if world > 1:
         dist.destroy_process_group()
+
+
+def case_in_mb(w, heads):
+    es = 2
+    return heads * ((4 * w["n_q"] + 4 * w["n_k"]) * w["d"] * es + 4 * w["n_q"]) / 1e6
 
 
 if __name__ == "__main__":

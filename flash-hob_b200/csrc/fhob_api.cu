@@ -4,6 +4,7 @@
 // (fhog/triton_bwdbwd.py:557-648).
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "fhob_common.cuh"
 
@@ -26,13 +27,23 @@ namespace {
 template <typename T>
 __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
                                float* __restrict__ nlc, float* __restrict__ k1, int* status, long rows, int d,
-                               int n_q) {
+                               int n_q, int first_live_query) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
   long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   int lane = threadIdx.x & 31;
   // the inputs are dense (bh*n_q rows), the row vectors are padded per head
   const long vrow = (row / n_q) * row_stride(n_q) + row % n_q;
+  if (row % n_q < first_live_query) {
+    // a query the causal mask leaves without any visible key (n_k < n_q): every P of its row is
+    // masked to zero in the passes, so the row contributes nothing and its dQ2 and ddO are zero.
+    // Its saved L (-inf) and O (0 or NaN, depending on who produced them) are not looked at.
+    if (lane == 0) {
+      nlc[vrow] = 0.f;
+      k1[vrow] = 0.f;
+    }
+    return;
+  }
   if (o == nullptr) {
     // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
     if (lane == 0) nlc[vrow] = -lse[row] * kLog2e;
@@ -61,6 +72,28 @@ __global__ void row_stats_kernel(const float* k1, const float* ndd, const float*
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Status word of the library itself: receives the device-side conditions of fhob_forward calls
+// that pass no workspace.  In host code the symbol is a handle, not a device address, so the
+// address each device gave it is looked up once, with that device current.
+__device__ int g_own_status;
+constexpr int kMaxDevices = 64;
+std::mutex g_own_status_mutex;
+int* g_own_status_ptr[kMaxDevices] = {};
+
+int own_status_word(int** out) {
+  int dev = -1;
+  FHOB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return FHOB_ERR_ARG;
+  std::lock_guard<std::mutex> lock(g_own_status_mutex);
+  if (!g_own_status_ptr[dev]) {
+    void* ptr = nullptr;
+    FHOB_CUDA_OK(cudaGetSymbolAddress(&ptr, g_own_status));
+    g_own_status_ptr[dev] = static_cast<int*>(ptr);
+  }
+  *out = g_own_status_ptr[dev];
+  return FHOB_OK;
+}
 
 // `o_optional`: the caller may leave p->o NULL (D is then taken from sum_j P dP inside the sweep
 // that yields dd and b, which only the tensor-core path does)
@@ -150,18 +183,20 @@ static int run_prepass(const FhobProblem* p, void* stream) {
   long rows = static_cast<long>(p->bh) * p->n_q;
   const int warps = 8;
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  // bottom-right aligned causal mask: query i sees key 0 only if i + n_k - n_q >= 0
+  const int first_live = (p->causal && p->n_q > p->n_k) ? p->n_q - p->n_k : 0;
   if (p->dtype == FHOB_BF16) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
-        rv.status, rows, p->d, p->n_q);
+        rv.status, rows, p->d, p->n_q, first_live);
   } else if (p->dtype == FHOB_F16) {
     prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
                                                        static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                       rv.status, rows, p->d, p->n_q);
+                                                       rv.status, rows, p->d, p->n_q, first_live);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                      rv.status, rows, p->d, p->n_q);
+                                                      rv.status, rows, p->d, p->n_q, first_live);
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
@@ -221,10 +256,18 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
 }
 
 int fhob_read_status(const FhobProblem* p, void* stream) {
-  if (!p || !p->workspace) return FHOB_ERR_WORKSPACE;
+  if (!p) return FHOB_ERR_ARG;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const void* word = p->workspace;
+  if (!word) {
+    // no workspace: the library's own word, which fhob_forward uses in that case
+    int* own = nullptr;
+    int st = own_status_word(&own);
+    if (st != FHOB_OK) return st;
+    word = own;
+  }
   int host = 0;
-  FHOB_CUDA_OK(cudaMemcpyAsync(&host, p->workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  FHOB_CUDA_OK(cudaMemcpyAsync(&host, word, sizeof(int), cudaMemcpyDeviceToHost, s));
   FHOB_CUDA_OK(cudaStreamSynchronize(s));
   return host;
 }
@@ -244,7 +287,7 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
 }
 
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream) {
-  if (!p || !p->q || !p->k || !p->v || !o_out || !lse_out) return FHOB_ERR_ARG;
+  if (!p || !p->q || !p->k || !p->v || !lse_out) return FHOB_ERR_ARG;
   if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->window < 0 || (p->window > 0 && p->causal != 1)) return FHOB_ERR_ARG;
@@ -254,11 +297,15 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
                      tc_first_order_supported(*p);
   if (p->impl == FHOB_IMPL_TCGEN05 && !tc_ok) return FHOB_ERR_SHAPE;
   if (p->impl != FHOB_IMPL_SIMT && tc_ok) {
-    if (p->workspace) {
+    int* status = static_cast<int*>(p->workspace);
+    if (status) {
       if ((reinterpret_cast<uintptr_t>(p->workspace) & 255u) || p->workspace_bytes < sizeof(int)) return FHOB_ERR_WORKSPACE;
-      FHOB_CUDA_OK(cudaMemsetAsync(p->workspace, 0, sizeof(int), s));  // status word
+    } else {
+      int st = own_status_word(&status);
+      if (st != FHOB_OK) return st;
     }
-    return tc_forward(*p, o_out, lse_out, s);
+    FHOB_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));  // every call starts with a clean status word
+    return tc_forward(*p, o_out, lse_out, status, s);
   }
   return simt_forward(*p, o_out, lse_out, s);
 }

@@ -113,7 +113,7 @@ int tc_pass(int pass, const FhobProblem& p, cudaStream_t s);
 
 // tensor-core forward (O, L) and first backward (dQ, dK, dV): tc_first_order.cu
 bool tc_first_order_supported(const FhobProblem& p);
-int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s);
+int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s);
 int tc_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s);
 int tc_selftest_expired_wait(int* status, cudaStream_t s);
 

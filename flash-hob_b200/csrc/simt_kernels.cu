@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 #pragma unroll
     for (int m = 0; m < DCH; ++m) {
       int col = lane + 32 * m;
-      if (col < d) st_elem<T>(o_out, qoff + static_cast<size_t>(qi) * d + col, acc[i][m] * inv);
+      if (col < d && o_out) st_elem<T>(o_out, qoff + static_cast<size_t>(qi) * d + col, acc[i][m] * inv);
     }
     if (lane == 0)
       lse_out[static_cast<size_t>(bh) * p.n_q + qi] =

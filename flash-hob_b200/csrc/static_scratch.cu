@@ -61,3 +61,17 @@ extern "C" int fhob_bwdbwd_static_scratch(const FhobProblem* p, void* stream) {
   // every row vector entry a pass reads was written earlier in the same call.
   return fhob_bwdbwd(&q, stream);
 }
+
+
+// The device status word of the built-in array (its first four bytes), for the current device.
+// Synchronises `stream`; allocates nothing.
+extern "C" int fhob_static_scratch_status(void* stream) {
+  void* scratch = nullptr;
+  int st = scratch_for_current_device(&scratch);
+  if (st != FHOB_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int host = 0;
+  FHOB_CUDA_OK(cudaMemcpyAsync(&host, scratch, sizeof(int), cudaMemcpyDeviceToHost, s));
+  FHOB_CUDA_OK(cudaStreamSynchronize(s));
+  return host;
+}

@@ -15,25 +15,23 @@
 //        reference maximum that follows the running row maximum lazily (only when it has grown by
 //        more than 8 in the log2 domain); on those occasions the threads rescale their part of O
 //        in TMEM, which is idle between two P V products.  Writes O and L.
-//   LSE  (queries stationary, 128 keys per tile): S = Q K^T; online log-sum-exp -> L (fp32)
-//   FWD  (queries stationary, 128 keys per tile): P = exp(S*scale - L);  O += P V
+//   LSE  (queries stationary, 128 keys per tile): S = Q K^T; online log-sum-exp -> L (fp32) only,
+//        for callers that need the logsumexp but not O (role of the reference's produce_L)
 //   BQ   (queries stationary,  64 keys per tile): dS = P (dP - D), dP = dO V^T;  dQ += dS K
 //   BK   (keys stationary,  64 queries per tile): transposed tiles;  dV += P^T dO, dK += dS^T Q
-// The forward is ONE; with FHOB_FORWARD_TWO_SWEEPS set in the environment it runs LSE then FWD
-// instead (the scores are computed twice, but no accumulator is ever rescaled).  The backward
-// follows jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
+// The backward follows jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
 #include "tc_common.cuh"
 
 namespace fhob {
 namespace {
 
-enum { FO_LSE = 0, FO_FWD = 1, FO_BQ = 2, FO_BK = 3, FO_ONE = 4 };
+enum { FO_LSE = 0, FO_BQ = 2, FO_BK = 3, FO_ONE = 4 };
 constexpr int FO_TAIL = 3072;  // barriers, TMEM base, abort flag, (max, sum) exchange
 
 template <int MODE, int D>
 struct FoCfg {
   static constexpr bool kQStat = MODE != FO_BK;
-  static constexpr bool kForward = MODE == FO_LSE || MODE == FO_FWD || MODE == FO_ONE;
+  static constexpr bool kForward = MODE == FO_LSE || MODE == FO_ONE;
   static constexpr int BN = kForward ? 128 : 64;
   static constexpr int NSTAT = kForward ? 1 : 2;         // Q | Q | Q, dO | K, V
   static constexpr int NSTRM = MODE == FO_LSE ? 1 : 2;   // K | K, V | K, V | Q, dO
@@ -58,11 +56,10 @@ struct FoCfg {
 struct FoParams {
   CUtensorMap stat[2];
   CUtensorMap strm[2];
-  const float* lse;   // FWD: L (natural log) of the stationary queries
   const float* nlc;   // BQ, BK: -L*log2(e) per query
   const float* k1;    // BQ, BK: -D per query
   float* lse_out;     // LSE
-  uint16_t* out0;     // FWD: O;  BQ: dQ;  BK: dK
+  uint16_t* out0;     // ONE: O;  BQ: dQ;  BK: dK
   uint16_t* out1;     // BK: dV
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
@@ -87,9 +84,6 @@ struct FoBars {
 };
 static_assert(sizeof(FoBars) <= FO_TAIL, "tail");
 
-// status word used when the caller passes no workspace
-__device__ int g_fo_status;
-
 template <int MODE, int D, bool F16>
 __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__ FoParams p) {
   using C = FoCfg<MODE, D>;
@@ -100,7 +94,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
   uint8_t* stat_tiles = smem;
   uint8_t* strm_tiles = smem + C::NSTAT * C::STAT_BYTES;
   FoBars* bars = reinterpret_cast<FoBars*>(strm_tiles + C::NSLOT * C::SLOT_BYTES);
-  int* status = p.status ? p.status : &g_fo_status;
+  int* status = p.status;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x / p.tiles_per_head;
@@ -282,9 +276,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
             const uint32_t sl = strm_lo + slot * kSlot16;
             const bool accum = it > 0;
-            if (MODE == FO_FWD || MODE == FO_ONE) {
+            if (MODE == FO_ONE) {
               gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
-              if (MODE == FO_ONE) commit(&bars->o_done);
+              commit(&bars->o_done);
             } else if (MODE == FO_BQ) {
               gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
             } else {
@@ -316,8 +310,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
     const float sl2 = p.scale * kLog2e;
     float r_nlc = 0.f, r_k1 = 0.f;
     if (kQStat && g_row < p.n_q) {
-      // L is the caller's dense tensor; the workspace vectors are padded per head
-      if (MODE == FO_FWD) r_nlc = -p.lse[static_cast<size_t>(head) * p.n_q + g_row] * kLog2e;
       if (MODE == FO_BQ) {
         const size_t vi = static_cast<size_t>(head) * row_stride(p.n_q) + g_row;
         r_nlc = p.nlc[vi];
@@ -469,32 +461,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[stage]);
-      } else if (MODE == FO_FWD) {
-        uint32_t w[2][16], xx[2][32];
-        tmem_ld32(acc, xx[0]);
-        tmem_ld32(acc + 32, xx[1]);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const uint32_t (&x)[32] = xx[c];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float2 arg = __ffma2_rn(f2(x[j], x[j + 1]), make_float2(sl2, sl2), make_float2(r_nlc, r_nlc));
-            float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
-            if (masked) {
-              const int idx = col_base + 32 * c + j;
-              pr.x = (idx >= lo && idx <= hi) ? pr.x : 0.f;
-              pr.y = (idx + 1 >= lo && idx + 1 <= hi) ? pr.y : 0.f;
-            }
-            w[c][j / 2] = pack16<F16>(pr.x, pr.y);
-          }
-        }
-        // the 16-bit tile overwrites accumulator columns this thread has already consumed
-        tmem_st16(acc, w[0]);
-        tmem_st16(acc + 16, w[1]);
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&bars->p_full[stage]);
       } else {
         uint32_t s[32], dp[32], w_p[16], w_ds[16];
         tmem_ld32(acc, s);
@@ -574,7 +540,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
                           (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
           // dS was stored without the scale; the single-sweep forward divides by the row sum here
-          const float mul = MODE == FO_ONE ? inv_l : ((o == 0 && MODE != FO_FWD) ? p.scale : 1.f);
+          const float mul = MODE == FO_ONE ? inv_l : (o == 0 ? p.scale : 1.f);
 #pragma unroll
           for (int ch = 0; ch < D / 32; ++ch) {
             uint32_t v[16];
@@ -649,19 +615,14 @@ int check_device() {
 }
 
 template <int D, bool F16>
-int forward_impl(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s) {
+int forward_impl(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   FoParams tp;
   memset(&tp, 0, sizeof(tp));
-  tp.status = p.workspace ? static_cast<int*>(p.workspace) : nullptr;
+  tp.status = status;
   tp.lse_out = lse_out;
   tp.out0 = static_cast<uint16_t*>(o_out);
-  static const bool two_sweeps = getenv("FHOB_FORWARD_TWO_SWEEPS") != nullptr;
-  if (!two_sweeps) return fo_launch<FO_ONE, D, F16>(p, tp, s);
-  // the order-independent variant: log-sum-exp first, then exp(S - L) V
-  int st = fo_launch<FO_LSE, D, F16>(p, tp, s);
-  if (st != FHOB_OK) return st;
-  tp.lse = lse_out;
-  return fo_launch<FO_FWD, D, F16>(p, tp, s);
+  // no O wanted: the scores alone, reduced to the logsumexp
+  return o_out ? fo_launch<FO_ONE, D, F16>(p, tp, s) : fo_launch<FO_LSE, D, F16>(p, tp, s);
 }
 
 template <int D, bool F16>
@@ -706,13 +667,15 @@ int tc_selftest_expired_wait(int* status, cudaStream_t s) {
 
 bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p); }
 
-int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t s) {
+int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;
   int st = check_device();
   if (st != FHOB_OK) return st;
   if (p.dtype == FHOB_F16)
-    return p.d == 64 ? forward_impl<64, true>(p, o_out, lse_out, s) : forward_impl<128, true>(p, o_out, lse_out, s);
-  return p.d == 64 ? forward_impl<64, false>(p, o_out, lse_out, s) : forward_impl<128, false>(p, o_out, lse_out, s);
+    return p.d == 64 ? forward_impl<64, true>(p, o_out, lse_out, status, s)
+                     : forward_impl<128, true>(p, o_out, lse_out, status, s);
+  return p.d == 64 ? forward_impl<64, false>(p, o_out, lse_out, status, s)
+                   : forward_impl<128, false>(p, o_out, lse_out, status, s);
 }
 
 int tc_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s) {

@@ -93,21 +93,8 @@ struct TcParams {
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
   float scale;
-#ifdef FHOB_TC_PROFILE
-  unsigned long long* prof;
-#endif
 };
 
-// Optional cycle accounting of the three roles (compile with -DFHOB_TC_PROFILE; development aid).
-#ifdef FHOB_TC_PROFILE
-#define PROF_DECL long long prof_t[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long prof_t0 = clock64();
-#define PROF_MARK(i) { long long now__ = clock64(); prof_t[i] += now__ - prof_t0; prof_t0 = now__; }
-#define PROF_FLUSH(base) for (int i__ = 0; i__ < 8; ++i__) atomicAdd(&p.prof[(base) + i__], (unsigned long long)prof_t[i__]);
-#else
-#define PROF_DECL
-#define PROF_MARK(i)
-#define PROF_FLUSH(base)
-#endif
 
 struct Bars {
   uint64_t stat_full;
@@ -396,12 +383,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           tma_load_3d(stat_tiles + i * C::STAT_BYTES + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
                       head);
       int issued = 0;
-      PROF_DECL
       for (int it = 0; it < n_iter; ++it) {
         const int slot = it % C::NSLOT;
-        PROF_MARK(7)
         if (!wait_bar(&bars->strm_free[slot], ((it / C::NSLOT) & 1) ^ 1, bars, p.status)) break;
-        PROF_MARK(0)
         mbar_arrive_expect_tx(&bars->strm_full[slot], C::SLOT_BYTES);
         uint8_t* dst = strm_tiles + slot * C::SLOT_BYTES;
         const int n0 = (t_begin + it) * BN;
@@ -418,9 +402,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           bulk_load(sv + 3 * BN * 4, p.k23 + vo, BN * 4, &bars->strm_full[slot]);
         }
         issued = it + 1;
-        PROF_MARK(1)
       }
-      PROF_FLUSH(16)
       // drain: every load issued above must have landed before the CTA may exit
       wait_bar(&bars->stat_full, 0, bars, p.status);
       for (int it = issued > C::NSLOT ? issued - C::NSLOT : 0; it < issued; ++it) {
@@ -462,16 +444,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         return slot_lo - (1u << 16) + (C::strm_base(i) >> 4) + (static_cast<uint32_t>(C::strm_box(i) >> 4) << 16);
       };
       bool ok = wait_all(&bars->stat_full, 0);
-      PROF_DECL
 
       // score-shaped products of this chain for tile `it` (waits for the tile's shared-memory slot)
       //   chain 0, group A: [S | stat0.strm1^T] as one N = 2*BN product, then A2 += stat1.strm0^T
       //   chain 1, group B: [dP | X] (one stacked product in passes 2, 3; two products in pass 4)
       auto issue_scores = [&](int it, uint32_t acc) -> bool {
         const int slot = it % C::NSLOT;
-        PROF_MARK(7)
         if (!wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1)) return false;
-        PROF_MARK(0)
         tc_fence_after();
         const uint32_t sl = strm_lo + slot * kSlot16;
         if (chain == 0) {
@@ -497,14 +476,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         for (int it = 0; ok && it < n_iter; ++it) {
           const int stage = it % C::NSS;
           const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
-          PROF_MARK(7)
           ok = wait_all(&bars->s_free[stage], ((it / C::NSS) & 1) ^ 1);
-          PROF_MARK(1)
           ok = ok && issue_scores(it, acc);
           if (!ok) break;
           commit(&bars->s_full[stage]);
           commit(&bars->strm_free[it % C::NSLOT]);
-          PROF_MARK(2)
         }
       } else {
         // One TMEM stage, pipelined per chain: scores(t) -> [elementwise half] -> outputs(t) ->
@@ -514,14 +490,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         const uint32_t out0 = tmem_base, out1 = tmem_base + D;
         ok = ok && issue_scores(0, acc);
         if (ok) commit(&bars->s_full[chain]);
-        PROF_MARK(2)
         for (int it = 0; ok && it < n_iter; ++it) {
           const uint32_t sl = strm_lo + (it % C::NSLOT) * kSlot16;
           const bool accum = it > 0;
-          PROF_MARK(7)
           ok = wait_all(&bars->p_full[chain], it & 1);
           if (!ok) break;
-          PROF_MARK(3)
           tc_fence_after();
           if (chain == 0) {
             gemm_ts<D, BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o, accum);              // ddP . V | dO
@@ -531,7 +504,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             gemm_ts<D, BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o, true);   // dS2 . K   | Q
           }
           commit(&bars->strm_free[it % C::NSLOT]);
-          PROF_MARK(4)
           // Chain 1's group A of the next tile gates the next elementwise half, while chain 2's
           // group B is needed half a tile later: chain 2 lets chain 1 issue first, so the tensor
           // pipe runs them in that order.
@@ -539,19 +511,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             ok = wait_all(&bars->chain_go, it & 1);
             if (!ok) break;
           }
-          PROF_MARK(5)
           if (it + 1 < n_iter) {
             ok = issue_scores(it + 1, acc);
             if (!ok) break;
             commit(&bars->s_full[chain]);
           }
           if (chain == 0 && leader) mbar_arrive(&bars->chain_go);
-          PROF_MARK(6)
         }
       }
-#ifdef FHOB_TC_PROFILE
-      if (leader && chain == 0) PROF_FLUSH(8)
-#endif
       if (ok) {
         if (PASS >= 3) commit(&bars->out_full);
       } else {
@@ -633,7 +600,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
     float2 racc[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
     float2& rowacc = racc[0];
     bool ok = true;
-    PROF_DECL
 
     for (int it = 0; it < n_iter; ++it) {
       const int n0 = (t_begin + it) * BN;
@@ -651,18 +617,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       const int col_base = n0 + half * (BN / 2);
       if constexpr (PASS <= 2) {
         const int stage = it % C::NSS;
-        PROF_MARK(7)
         ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[stage], (it / C::NSS) & 1, bars, p.status));
         if (!ok) break;
-        PROF_MARK(0)
         tc_fence_after();
         const uint32_t acc = tmem_base + lane_base + stage * C::STAGE_COLS + half * (BN / 2);
         if (masked) ew_reduce<PASS, BN, true, FUSED>(acc, col_base, c, racc);
         else ew_reduce<PASS, BN, false, FUSED>(acc, col_base, c, racc);
-        PROF_MARK(1)
         tc_fence_before();
         mbar_arrive(&bars->s_free[stage]);
-        PROF_MARK(2)
       } else {
         const uint32_t acc = tmem_base + lane_base + C::OUT_COLS + half * (BN / 2);
         float2 ps[16], tt[16];
@@ -673,10 +635,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           if (!ok) break;
           c.sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::NSTRM * C::STRM_BYTES);
         }
-        PROF_MARK(7)
         ok = __all_sync(0xffffffffu, wait_bar(early_s(PASS) ? &bars->s_ready : &bars->s_full[0], it & 1, bars, p.status));
         if (!ok) break;
-        PROF_MARK(0)
         tc_fence_after();
         if (masked) ok = ew_half_a<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
         else ok = ew_half_a<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
@@ -684,25 +644,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[0]);
-        PROF_MARK(1)
         ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[1], it & 1, bars, p.status));
         if (!ok) break;
-        PROF_MARK(4)
         tc_fence_after();
         if (masked) ew_half_b<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
         else ew_half_b<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[1]);
-        PROF_MARK(2)
       }
     }
-#ifdef FHOB_TC_PROFILE
-    if (threadIdx.x == EW_WARP0 * 32) {
-      prof_t[3] = n_iter;
-      PROF_FLUSH(0)
-    }
-#endif
 
     // ---- results
     if (FUSED) {
@@ -792,13 +743,6 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
 // ------------------------------------------------------------------ host side
 
-// Streamed-tile height of pass 1 (the other passes use 64 rows).  128 rows let the stacked
-// [K ; ddK] operand reach N = 256; FHOB_TC_BN1=64 selects the smaller tile for experiments.
-int env_int(const char* name, int dflt) {
-  const char* v = getenv(name);
-  return v ? atoi(v) : dflt;
-}
-
 template <int PASS, int D, int BN, int FUSED = 0, bool F16 = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, D, BN>;
@@ -827,35 +771,16 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
   const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
   if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
-#ifdef FHOB_TC_PROFILE
-  static unsigned long long* prof_dev = nullptr;
-  if (!prof_dev) FHOB_CUDA_OK(cudaMalloc(&prof_dev, 24 * sizeof(unsigned long long)));
-  FHOB_CUDA_OK(cudaMemsetAsync(prof_dev, 0, 24 * sizeof(unsigned long long), s));
-  tp.prof = prof_dev;
-#endif
   kernel<<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
   FHOB_CUDA_OK(cudaGetLastError());
-#ifdef FHOB_TC_PROFILE
-  if (getenv("FHOB_TC_PROF_PRINT")) {
-    unsigned long long h[24];
-    FHOB_CUDA_OK(cudaMemcpyAsync(h, prof_dev, sizeof(h), cudaMemcpyDeviceToHost, s));
-    FHOB_CUDA_OK(cudaStreamSynchronize(s));
-    const double it = h[3] > 0 ? static_cast<double>(h[3]) : 1.0;  // tile iterations summed over CTAs
-    fprintf(stderr, "[prof] pass %d D %d BN %d cycles/tile-iter | EW:", PASS, D, BN);
-    for (int i = 0; i < 8; ++i) if (i != 3) fprintf(stderr, " e%d=%.0f", i, h[i] / it);
-    fprintf(stderr, " | MMA:");
-    for (int i = 0; i < 8; ++i) fprintf(stderr, " m%d=%.0f", i, h[8 + i] / it);
-    fprintf(stderr, " | TMA: wait_free=%.0f issue=%.0f other=%.0f\n", h[16] / it, h[17] / it, h[23] / it);
-  }
-#endif
   return FHOB_OK;
 }
 
 template <int D, bool F16>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
-  static const int bn1 = env_int("FHOB_TC_BN1", 128);
   switch (pass) {
-    case 1: return bn1 == 64 ? launch<1, D, 64, 0, F16>(p, s) : launch<1, D, 128, 0, F16>(p, s);
+    // pass 1 streams 128-row tiles (the stacked [K ; ddK] operand reaches N = 256), the others 64
+    case 1: return launch<1, D, 128, 0, F16>(p, s);
     case 2: return launch<2, D, 64, 0, F16>(p, s);
     case 12: return launch<2, D, 64, 1, F16>(p, s);  // passes 1 and 2 in one sweep
     case 13: return launch<2, D, 64, 2, F16>(p, s);  // the same, also producing D = sum P dP (no O given)

@@ -4,10 +4,7 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
-import os
-
-# FHOB_LIB_PATH points at an alternative build of the same library (e.g. an instrumented one)
-LIB_PATH = Path(os.environ.get("FHOB_LIB_PATH") or Path(__file__).resolve().parent / "libfhob.so")
+LIB_PATH = Path(__file__).resolve().parent / "libfhob.so"
 
 FHOB_BF16, FHOB_F32, FHOB_F16 = 0, 1, 2
 DTYPES = {"torch.bfloat16": FHOB_BF16, "torch.float32": FHOB_F32, "torch.float16": FHOB_F16}
@@ -19,7 +16,7 @@ SYMBOLS = (
     "fhob_version", "fhob_strerror", "fhob_last_cuda_error", "fhob_workspace_bytes", "fhob_bwdbwd",
     "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
     "fhob_read_status", "fhob_forward", "fhob_backward", "fhob_bwdbwd_static_scratch",
-    "fhob_selftest_expired_wait", "fhob_visible_tiles",
+    "fhob_selftest_expired_wait", "fhob_visible_tiles", "fhob_static_scratch_status",
 )
 STATIC_SCRATCH_MAX_ROWS = 262144
 
@@ -69,6 +66,8 @@ def load() -> C.CDLL:
     lib.fhob_visible_tiles.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int), C.POINTER(C.c_int)]
     lib.fhob_selftest_expired_wait.restype = C.c_int
     lib.fhob_selftest_expired_wait.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    lib.fhob_static_scratch_status.restype = C.c_int
+    lib.fhob_static_scratch_status.argtypes = [C.c_void_p]
     lib.fhob_forward.restype = C.c_int
     lib.fhob_forward.argtypes = [P, C.c_void_p, C.c_void_p, C.c_void_p]
     _lib = lib

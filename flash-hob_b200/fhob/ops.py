@@ -154,7 +154,7 @@ def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check,
 
 
 def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = False,
-                 sliding_window: Optional[int] = None, impl: str = "auto", check: bool = False,
+                 sliding_window: Optional[int] = None, impl: str = "auto", check: Optional[bool] = None,
                  device: Optional[torch.device] = None, out=None, workspace=None) -> Tuple[torch.Tensor, ...]:
     """Double backward of scaled-dot-product attention.
 
@@ -172,49 +172,79 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     none; its oracle does: jax_refs/flash_impl.py:86-91); ``sliding_window``
     the oracle's ``sliding_window_length`` W (needs ``is_causal``): query i
     then sees only the W keys that end at its causal diagonal; ``impl`` one of
-    "auto", "simt", "tcgen05"; ``check`` synchronise and raise if a device
-    wait timed out; ``out`` a tuple ``(dQ2, dK2, dV2, ddO)`` of preallocated
-    contiguous device tensors to write into and ``workspace`` a uint8 device
-    tensor of ``fhob_workspace_bytes`` bytes (the reference allocates both per
-    call, :581-584, :617-618; with them given the call allocates nothing).
+    "auto", "simt", "tcgen05"; ``check`` read the device status word after
+    the kernels and raise if a bounded device wait ran out.  Reading it
+    synchronises the stream, so the default is ``False`` for device tensors
+    (the call stays asynchronous; a wait that ran out - which only a hardware
+    or driver fault can cause - would then go unnoticed and leave wrong
+    results) and ``True`` for host tensors, where the call synchronises anyway;
+    ``out`` a tuple ``(dQ2, dK2, dV2, ddO)`` of preallocated contiguous tensors
+    to write into and ``workspace`` a uint8 device tensor of
+    ``fhob_workspace_bytes`` bytes (the reference allocates both per call,
+    :581-584, :617-618; with them given a device call allocates nothing).
+
+    With ``is_causal`` and N_K < N_Q the first N_Q - N_K queries see no key:
+    their dQ2 and ddO rows are zero and their rows of ``O`` and ``L`` are not
+    read (the reference leaves this case undefined).
 
     Host (CPU) tensors are accepted too: they are staged to ``device``
-    (default: current CUDA device) on the current stream, preferably from
-    pinned memory, and the four results come back as pinned host tensors after
-    a stream synchronise.
+    (default: current CUDA device) in head ranges, preferably from pinned
+    memory, and the four results come back as pinned host tensors (or in
+    ``out``, four host tensors, preferably pinned) after a stream synchronise.
     """
     if Q.device.type == "cuda":
-        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check, sliding_window, out,
-                           workspace)
+        return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, bool(check), sliding_window,
+                           out, workspace)
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
-    if O is None or out is not None or workspace is not None:
-        raise ValueError("O=None, out= and workspace= are only supported for device tensors")
+    if O is None or workspace is not None:
+        raise ValueError("O=None and workspace= are only supported for device tensors")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check, dev, window=sliding_window)
+    return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check is None or bool(check), dev,
+                     window=sliding_window, out=out)
 
 
 _copy_streams: dict = {}
+HOST_RANGE_BYTES = 96 << 20   # input bytes staged per head range on the host-buffer path
 
 
-def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8, window=None):
+def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None, range_bytes=None):
     """Host tensors in, pinned host tensors out.  Heads are independent, so the batch is cut into
-    up to `max_chunks` head ranges that flow through three streams: upload of range i+1, the
-    kernels of range i and the download of range i-1 overlap."""
+    head ranges of about ``HOST_RANGE_BYTES`` of input each (at least four ranges when there are
+    that many heads) that flow through three streams: upload of range i+1, the kernels of range i
+    and the download of range i-1 overlap.  Device staging memory comes from torch's caching
+    allocator, so after the first call of a shape nothing is allocated on the device, and the
+    results' pinned buffers come from torch's caching host allocator."""
+    names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
     shape_q, shape_k = mats[0].shape, mats[1].shape
-    mats3 = [_fold(t, n) for t, n in zip(mats, ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV"))]
+    mats3 = [_fold(t, n) for t, n in zip(mats, names)]
     bh = mats3[0].shape[0]
     lse = (L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)).to(torch.float32)
     if lse.shape[0] != bh:
         raise ValueError(f"L: expected {bh} rows, got {tuple(L.shape)}")
-    outs_host = [torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
-                 for t in (mats3[0], mats3[1], mats3[1], mats3[0])]
+    want = (mats3[0], mats3[1], mats3[1], mats3[0])
+    if out is None:
+        outs_host = [torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True) for t in want]
+    else:
+        if len(out) != 4:
+            raise ValueError("out: expected (dQ2, dK2, dV2, ddO)")
+        outs_host = []
+        for n, t, w in zip(("dQ2", "dK2", "dV2", "ddO"), out, want):
+            if t.device.type != "cpu" or t.dtype != w.dtype or not t.is_contiguous() or t.numel() != w.numel():
+                raise ValueError(f"out {n}: need a contiguous host {w.dtype} tensor of {tuple(w.shape)} elements")
+            outs_host.append(t.view(w.shape))
     main = torch.cuda.current_stream(dev)
     up, down = _copy_streams.setdefault(dev.index, (torch.cuda.Stream(dev), torch.cuda.Stream(dev)))
     up.wait_stream(main)
-    n_chunks = max(1, min(max_chunks, bh))
+    head_bytes = sum(t[0].numel() * t.element_size() for t in mats3) + lse[0].numel() * 4
+    per_range = max(1, int(range_bytes or HOST_RANGE_BYTES) // max(1, head_bytes))
+    n_chunks = max(-(-bh // per_range), min(bh, 4))
     bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
-    for lo, hi in zip(bounds, bounds[1:]):
+    widest = max(hi - lo for lo, hi in zip(bounds, bounds[1:]))
+    ws = _workspace(dev, main.cuda_stream, _lib.load().fhob_workspace_bytes(widest, mats3[0].shape[1]))
+    # the pre-pass of every range clears the status word, so each range's word is kept
+    status_host = torch.zeros(n_chunks, dtype=torch.int32, pin_memory=True) if check else None
+    for i, (lo, hi) in enumerate(zip(bounds, bounds[1:])):
         with torch.cuda.stream(up):
             staged = [t[lo:hi].to(dev, non_blocking=True) for t in mats3 + [lse]]
             ready = torch.cuda.Event()
@@ -222,7 +252,9 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8, 
         main.wait_event(ready)
         for t in staged:
             t.record_stream(main)
-        res = _run_device(*staged, scale, is_causal, impl, check, window)  # check=True synchronises per range
+        res = _run_device(*staged, scale, is_causal, impl, False, window, workspace=ws)
+        if check:
+            status_host[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
         done = torch.cuda.Event()
         done.record(main)
         down.wait_event(done)
@@ -231,20 +263,27 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, max_chunks: int = 8, 
                 r.record_stream(down)
                 h[lo:hi].copy_(r.reshape(h[lo:hi].shape), non_blocking=True)
     down.synchronize()
+    if check:
+        main.synchronize()
+        for status in status_host.tolist():
+            _lib.check(status, "fhob_bwdbwd (device status)")
     return (outs_host[0].reshape(shape_q), outs_host[1].reshape(shape_k), outs_host[2].reshape(shape_k),
             outs_host[3].reshape(shape_q))
 
 
 def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None,
-                      impl: str = "auto"):
+                      impl: str = "auto", check: bool = False, need_o: bool = True):
     """O(N)-memory producer of the saved forward results: returns ``(O, L)``.
 
     ``O = softmax(Q K^T scale) V`` in the input dtype and the fp32 logsumexp
     ``L`` — the two tensors ``flash_bwdbwd`` consumes.  Role of the reference's
     forward kernel and ``produce_L`` (fhog/triton_flash.py:12-133, :252-258),
     which is dense, returns L in the input dtype and raises for causal masks.
-    16-bit inputs with D in {64, 128} run on the tensor cores (two sweeps: the
-    log-sum-exp, then ``exp(S - L) V``), everything else on CUDA cores.
+    16-bit inputs with D in {64, 128} run on the tensor cores (one sweep over
+    the keys with an online softmax), everything else on CUDA cores.
+    ``need_o=False`` skips the ``P V`` product and returns ``(None, L)``.
+    ``check`` synchronises and raises if a bounded device wait ran out.
+    Queries that see no key (causal with N_K < N_Q) get ``O = 0``, ``L = -inf``.
     """
     shape_q = Q.shape
     q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
@@ -253,7 +292,7 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     bh, n_q, d = q.shape
     if scale is None:
         scale = d ** -0.5
-    o = torch.empty_like(q)
+    o = torch.empty_like(q) if need_o else None
     lse = torch.empty(bh, n_q, dtype=torch.float32, device=q.device)
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
@@ -264,17 +303,22 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     p.window = _window(is_causal, sliding_window)
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
+    lib = _lib.load()
+    ws = _workspace(q.device, stream, 256)   # receives the status word
+    p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
-        _lib.check(_lib.load().fhob_forward(C.byref(p), C.c_void_p(o.data_ptr()), C.c_void_p(lse.data_ptr()),
-                                            C.c_void_p(stream)), "fhob_forward")
-    return o.reshape(shape_q), lse.reshape(shape_q[:-1])
+        _lib.check(lib.fhob_forward(C.byref(p), C.c_void_p(o.data_ptr() if need_o else None),
+                                    C.c_void_p(lse.data_ptr()), C.c_void_p(stream)), "fhob_forward")
+        if check:
+            _lib.check(lib.fhob_read_status(C.byref(p), C.c_void_p(stream)), "fhob_forward (device status)")
+    return (o.reshape(shape_q) if need_o else None), lse.reshape(shape_q[:-1])
 
 
 def produce_L(Q, K, is_causal: bool = False, scale=None, sliding_window: Optional[int] = None):
     """fp32 logsumexp of the scaled scores, same name and argument order as the
     reference helper (fhog/triton_flash.py:252-258) but O(N) memory, fp32 and
-    causal-capable."""
-    return attention_forward(Q, K, K, scale, is_causal=is_causal, sliding_window=sliding_window)[1]
+    causal-capable.  Only the scores are computed (no ``P V`` product)."""
+    return attention_forward(Q, K, K, scale, is_causal=is_causal, sliding_window=sliding_window, need_o=False)[1]
 
 
 def run_passes(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal=False, sliding_window=None, impl="auto",

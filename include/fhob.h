@@ -63,7 +63,10 @@ typedef struct FhobProblem {
   int32_t n_k;     /* key rows per head */
   int32_t d;       /* head dim, shared by q/k and v like the reference (:577) */
   int32_t dtype;   /* FHOB_BF16, FHOB_F16 or FHOB_F32 */
-  int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j */
+  int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j.
+                      With n_k < n_q the first n_q - n_k queries see no key at all: their dQ2 and ddO rows are
+                      zero, they add nothing to dK2 and dV2, and their lse / o entries are not read
+                      (fhob_forward writes lse = -inf and o = 0 there) */
   int32_t impl;    /* FHOB_IMPL_* */
   float scale;     /* softmax scale */
   int32_t window;  /* sliding_window_length of jax_refs/flash_impl.py:86-91: 0 = none; W > 0 (needs causal = 1)
@@ -154,7 +157,9 @@ int fhob_row_stats(const FhobProblem* p, float* d_out, float* dd_out, float* b_o
 
 /*
  * Synchronises `stream`, reads the device status word of the workspace and
- * returns it (0 = every bounded wait completed).  The reference has no
+ * returns it (0 = every bounded wait completed).  With p->workspace NULL it
+ * reads the library's own per-device word instead, which is where
+ * fhob_forward reports when it is given no workspace.  The reference has no
  * counterpart; its kernels cannot time out.
  */
 int fhob_read_status(const FhobProblem* p, void* stream);
@@ -190,9 +195,13 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
  * (fhog/triton_flash.py:12-133, :252-258), which is dense, rounds L to the
  * input type and refuses causal masks.  Uses p->q, k, v, scale, causal,
  * window, impl; writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).
+ * `o_out` may be NULL when only the logsumexp is wanted (the role of
+ * produce_L): the P V product is then skipped altogether.
  * 16-bit inputs with d in {64, 128} run on the tensor cores (impl AUTO or
- * TCGEN05), everything else on CUDA cores.  p->workspace may be NULL; when
- * given, its status word is cleared and receives device-side timeouts.
+ * TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
+ * that ran out) go to the status word at the start of p->workspace, or, when
+ * p->workspace is NULL, to a word the library keeps per device; either is
+ * cleared by the call and read with fhob_read_status(p, stream).
  */
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream);
 
@@ -236,11 +245,21 @@ int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stre
  * every entry before reading it, so nothing has to be reset between calls.
  * Because of the sharing, two calls whose kernels can overlap on the GPU (two
  * streams, two host threads on one device) race on the array: issue these
- * calls on one stream, or otherwise order them.  fhob_read_status() does not
- * see this array; a timed-out wait shows up as wrong results only.
+ * calls on one stream, or otherwise order them.  The array belongs to the
+ * calling thread's current device, so make the device that holds the tensors
+ * current before the call.  fhob_read_status() does not see this array; its
+ * status word is read with fhob_static_scratch_status().
  */
 #define FHOB_STATIC_SCRATCH_MAX_ROWS 262144
 int fhob_bwdbwd_static_scratch(const FhobProblem* p, void* stream);
+
+/*
+ * Synchronises `stream` and returns the device status word of the built-in
+ * scratch array on the current device (0 = every bounded wait of the last
+ * fhob_bwdbwd_static_scratch call completed).  Allocates nothing.  No
+ * counterpart in the reference.
+ */
+int fhob_static_scratch_status(void* stream);
 
 #ifdef __cplusplus
 }

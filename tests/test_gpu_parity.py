@@ -21,7 +21,21 @@ OUT_NAMES = ("dq2", "dk2", "dv2", "ddo")
 
 
 def _oracle(x64, scale, causal):
-    """fp64 oracle results + saved forward tensors, all (BH, N, D)."""
+    """fp64 oracle results + saved forward tensors, all (BH, N, D).
+
+    Causal with n_k < n_q: the first n_q - n_k queries see no key.  The oracle is evaluated on the
+    remaining queries (the mask is bottom-right aligned, so that is the same problem) and the
+    dead queries get zero result rows, L = -inf and O = 0, which is how the library defines them."""
+    nq, nk = x64["q"].shape[1], x64["k"].shape[1]
+    if causal and nk < nq:
+        dead = nq - nk
+        live = {n: (t[:, dead:] if n in ("q", "do", "ddq") else t) for n, t in x64.items()}
+        ref, lse, o, stats = _oracle(live, scale, causal)
+        z = torch.zeros_like(x64["q"][:, :dead])
+        ref = (torch.cat([z, ref[0]], 1), ref[1], ref[2], torch.cat([z, ref[3]], 1))
+        lse = torch.cat([torch.full((lse.shape[0], dead), -float("inf"), dtype=lse.dtype), lse], 1)
+        stats = tuple(torch.cat([z[:, :, 0], t], 1) for t in stats)
+        return ref, lse, torch.cat([z, o], 1), stats
     vals = list(x64.values())
     ref = O.bwdbwd_closed_form(*vals, scale, causal)
     lse = O.attn_lse(x64["q"], x64["k"], scale, causal)
@@ -49,8 +63,6 @@ SMALL = [(2, 128, 128, 64), (2, 128, 256, 64), (1, 256, 128, 128), (3, 96, 160, 
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("bh,nq,nk,d", SMALL)
 def test_fp32_cuda_core_path(bh, nq, nk, d, causal):
-    if causal and nk < nq:
-        pytest.skip("rows with no visible key are undefined in the oracle")
     x = make_inputs(bh, nq, nk, d, seed=21, dtype=torch.float64)
     got, ref, _ = _run(x, d ** -0.5, causal, torch.float32, "auto")
     for n, g, r in zip(OUT_NAMES, got, ref):
@@ -124,8 +136,6 @@ BF16_CASES = [(2, 128, 128, 64), (2, 256, 384, 64), (2, 384, 256, 128), (1, 128,
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("bh,nq,nk,d", BF16_CASES)
 def test_bf16_outputs(bh, nq, nk, d, causal, impl):
-    if causal and nk < nq:
-        pytest.skip("rows with no visible key are undefined in the oracle")
     x = make_inputs(bh, nq, nk, d, seed=41, dtype=torch.float64)
     got, ref, _ = _run(x, d ** -0.5, causal, torch.bfloat16, impl)
     for n, g, r in zip(OUT_NAMES, got, ref):
@@ -634,34 +644,80 @@ def test_bf16_without_saved_output(d, causal):
         fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], None, *rest, is_causal=causal, impl="simt")
 
 
-@pytest.mark.parametrize("variant", ["FHOB_FORWARD_TWO_SWEEPS"])
-def test_alternative_forward_kernels(variant):
-    """The library's default forward is the single-sweep online-softmax kernel; the two-sweep
-    kernels (log-sum-exp, then P V) stay selectable through the environment and must give the
-    same results.  The choice is read once per process, hence the child process."""
-    import os
-    import subprocess
-    import sys
-    code = r'''
-import sys, math, torch
-sys.path[:0] = [%r, %r, %r]
-import fhob
-from oracle import attn_oracle as O
-from conftest import make_inputs
-for (bh, nq, nk, d, causal, w) in [(2, 384, 640, 128, False, None), (2, 328, 328, 64, True, None), (1, 512, 700, 128, True, 150)]:
-    x = make_inputs(bh, nq, nk, d, seed=171, dtype=torch.float64)
+@pytest.mark.parametrize("impl", ["simt", "tcgen05"])
+def test_logsumexp_only_forward(impl):
+    """produce_L / need_o=False: the scores reduced to the fp32 logsumexp, no P V product
+    (role of produce_L, fhog/triton_flash.py:252-258, which is dense, bf16 and non-causal only)."""
+    import fhob
+    import math
+    for (bh, nq, nk, d, causal, w) in [(2, 384, 640, 128, False, None), (2, 328, 328, 64, True, None),
+                                       (1, 512, 700, 128, True, 150)]:
+        x = make_inputs(bh, nq, nk, d, seed=171, dtype=torch.float64)
+        scale = d ** -0.5
+        l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=math.inf if w is None else w)
+        q, k = x["q"].bfloat16().cuda(), x["k"].bfloat16().cuda()
+        o, lse = fhob.attention_forward(q, k, k, scale, is_causal=causal, sliding_window=w, impl=impl, need_o=False,
+                                        check=True)
+        assert o is None and lse.dtype == torch.float32
+        assert O.rel_err(lse, l_ref) < 1e-5, (bh, nq, nk, d, causal, w)
+    assert O.rel_err(fhob.produce_L(q, k, is_causal=True, scale=scale, sliding_window=150), l_ref) < 1e-5
+
+
+def _live_rows_oracle(x, scale, first_live, window=None):
+    """Oracle results of a causal problem with n_k < n_q: the first `first_live` queries see no
+    key, so the problem equals the one over the remaining queries (the mask is bottom-right
+    aligned), with zero rows for the dead queries in the query-shaped results."""
+    import math
+    w = math.inf if window is None else window
+    live = {n: (t[:, first_live:] if n in ("q", "do", "ddq") else t) for n, t in x.items()}
+    ref = O.bwdbwd_closed_form(*live.values(), scale, True, sliding_window_length=w)
+    pad = lambda t: torch.cat([torch.zeros_like(x["q"][:, :first_live]), t], dim=1)
+    return (pad(ref[0]), ref[1], ref[2], pad(ref[3])), live
+
+
+@pytest.mark.parametrize("dtype,impl,tol", [(torch.bfloat16, "tcgen05", TOL_BF16), (torch.bfloat16, "simt", TOL_BF16),
+                                            (torch.float32, "auto", TOL_F32)])
+@pytest.mark.parametrize("bh,nq,nk,d,window", [(2, 384, 256, 128, None), (1, 300, 90, 64, None), (2, 256, 128, 64, 40),
+                                               (1, 517, 130, 128, None)])
+def test_causal_queries_without_any_visible_key(bh, nq, nk, d, window, dtype, impl, tol):
+    """Causal with n_k < n_q: the first n_q - n_k queries see no key.  Their dQ2 and ddO rows are
+    exactly zero, they add nothing to dK2 and dV2, and whatever sits in their rows of O and L
+    (NaN and -inf here, what a softmax over an empty row gives) is not read.  The reference
+    leaves the case undefined (its operator has no causal mask, its oracle divides 0 by 0)."""
+    import fhob
+    first_live = nq - nk
+    x = make_inputs(bh, nq, nk, d, seed=311, dtype=torch.float64)
     scale = d ** -0.5
-    wl = math.inf if w is None else w
-    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=wl)
-    l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=wl)
-    o, lse = fhob.attention_forward(x["q"].bfloat16().cuda(), x["k"].bfloat16().cuda(), x["v"].bfloat16().cuda(),
-                                    scale, is_causal=causal, sliding_window=w, impl="tcgen05")
-    assert O.rel_err(o, o_ref) < 2e-2 and O.rel_err(lse, l_ref) < 1e-5, (bh, nq, nk, d, causal, w)
-print("ok")
-''' % (str(ROOT), str(ROOT / "flash-hob_b200"), str(ROOT / "tests"))
-    env = dict(os.environ, **{variant: "1"})
-    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0 and "ok" in out.stdout, out.stderr[-2000:]
+    ref, live = _live_rows_oracle(x, scale, first_live, window)
+    import math
+    wl = math.inf if window is None else window
+    o_live = O.attn_fwd(live["q"], live["k"], live["v"], scale, True, sliding_window_length=wl)
+    l_live = O.attn_lse(live["q"], live["k"], scale, True, sliding_window_length=wl)
+    o = torch.cat([torch.full_like(x["q"][:, :first_live], float("nan")), o_live], dim=1)
+    lse = torch.cat([torch.full((bh, first_live), -float("inf"), dtype=torch.float64), l_live], dim=1)
+    dev = {k: v.to(dtype).cuda() for k, v in x.items()}
+    kw = dict(is_causal=True, sliding_window=window, impl=impl)
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o.to(dtype).cuda(), dev["do"], dev["ddq"], dev["ddk"],
+                            dev["ddv"], lse.float().cuda(), scale, check=True, **kw)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert torch.isfinite(g).all(), n
+        assert O.rel_err(g, r) < tol, n
+    assert torch.count_nonzero(got[0][:, :first_live]) == 0 and torch.count_nonzero(got[3][:, :first_live]) == 0
+    # the library's own forward gives O = 0 and L = -inf on those rows, and the first backward zero dQ rows
+    o_dev, lse_dev = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **kw)
+    assert torch.count_nonzero(o_dev[:, :first_live]) == 0 and torch.isinf(lse_dev[:, :first_live]).all()
+    assert O.rel_err(o_dev[:, first_live:], o_live) < tol
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o_dev, dev["do"], lse_dev, scale, **kw)
+    first_ref = O.attn_bwd(live["q"], live["k"], live["v"], live["do"], scale, True, sliding_window_length=wl)
+    assert torch.count_nonzero(first[0][:, :first_live]) == 0
+    assert O.rel_err(first[0][:, first_live:], first_ref[0]) < tol
+    assert O.rel_err(first[1], first_ref[1]) < tol and O.rel_err(first[2], first_ref[2]) < tol
+    if dtype != torch.float32 and impl == "tcgen05":
+        # without the saved output (D from the sweep) the same holds
+        got2 = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], None, dev["do"], dev["ddq"], dev["ddk"], dev["ddv"],
+                                 lse.float().cuda(), scale, check=True, **kw)
+        for n, g, r in zip(OUT_NAMES, got2, ref):
+            assert torch.isfinite(g).all() and O.rel_err(g, r) < tol, n
 
 
 def test_preallocated_outputs_and_workspace():

@@ -23,8 +23,19 @@ from conftest import make_inputs
 from fhob import _lib
 
 
-def test_rows_beyond_capacity_are_refused():
-    lib = _lib.load()
+@pytest.fixture(scope="module")
+def lib():
+    """The library, built first when the tree is fresh (same fixture as the C-ABI tests)."""
+    import importlib.util
+    from conftest import ROOT
+    spec = importlib.util.spec_from_file_location("fhob_build", ROOT / "flash-hob_b200" / "build.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+    return _lib.load()
+
+
+def test_rows_beyond_capacity_are_refused(lib):
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = 65, 4096, 4096, 128          # 266240 rows > 262144
     assert p.bh * p.n_q > _lib.STATIC_SCRATCH_MAX_ROWS
@@ -34,15 +45,17 @@ def test_rows_beyond_capacity_are_refused():
 
 
 @pytest.mark.gpu
-def test_matches_regular_entry_point_on_two_calls_in_a_row():
+def test_matches_regular_entry_point_on_two_calls_in_a_row(lib):
     import fhob
     from fhob.ops import _Problem
     from oracle import attn_oracle as O
 
-    lib = _lib.load()
-    # second problem is smaller and causal, so stale row vectors of the first call would show
-    cases = [(4, 512, 768, 128, False, 101), (2, 256, 256, 64, True, 102)]
-    for bh, nq, nk, d, causal, seed in cases:
+    # The later problems are smaller than the first, causal, and have a ragged n_q (not a multiple
+    # of 4 or 64): their padded row-vector slices and the tail the key-tiled pass reads past the
+    # last head then hold the first call's values, which must not leak into the results.
+    cases = [(4, 512, 768, 128, False, 101), (2, 256, 256, 64, True, 102), (3, 130, 131, 128, True, 103),
+             (1, 99, 300, 64, True, 104)]
+    for i, (bh, nq, nk, d, causal, seed) in enumerate(cases):
         x = make_inputs(bh, nq, nk, d, seed=seed, dtype=torch.bfloat16, device="cuda")
         scale = d ** -0.5
         o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=causal)
@@ -51,9 +64,17 @@ def test_matches_regular_entry_point_on_two_calls_in_a_row():
 
         prob = _Problem(*args, causal, "auto")           # fresh output tensors + the argument struct
         prob.p.workspace, prob.p.workspace_bytes = None, 0   # must not be needed
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        torch_before = torch.cuda.memory_allocated()
         st = lib.fhob_bwdbwd_static_scratch(C.byref(prob.p), C.c_void_p(prob.stream))
         assert st == 0, lib.fhob_strerror(st)
-        torch.cuda.synchronize()
+        assert lib.fhob_static_scratch_status(C.c_void_p(prob.stream)) == 0     # synchronises the stream
+        if i > 0:
+            # the claim itself: once the device has been set up by the first call, a call takes no
+            # device memory, neither from the driver nor from torch's allocator
+            assert torch.cuda.mem_get_info()[0] == free_before
+            assert torch.cuda.memory_allocated() == torch_before
         got = prob.outputs()
         for name, g, w in zip(("dq2", "dk2", "dv2", "ddo"), got, want):
             assert O.rel_err(g, w.float()) < 2e-2, name      # the tolerance of the bf16 parity tests
