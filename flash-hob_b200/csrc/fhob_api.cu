@@ -103,7 +103,7 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;
   if (p->causal != 0 && p->causal != 1) return FHOB_ERR_ARG;
-  if (p->window < 0 || (p->window > 0 && !p->causal) || p->reserved != 0) return FHOB_ERR_ARG;
+  if (p->window < 0 || (p->window > 0 && !p->causal) || p->d_v < 0) return FHOB_ERR_ARG;
   const void* ins[] = {p->q, p->k, p->v, p->o, p->d_o, p->lse, p->ddq, p->ddk, p->ddv};
   for (int i = 0; i < (need_cotangents ? 9 : 6); ++i) {
     if (i == 3 && !ins[i] && o_optional && p->impl != FHOB_IMPL_SIMT && tc_supported(*p)) continue;
@@ -117,9 +117,10 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
       if (!aligned16(x)) return FHOB_ERR_ALIGN;
     }
   }
-  size_t row_bytes = static_cast<size_t>(p->d) * (p->dtype == FHOB_F32 ? 4 : 2);
-  if (row_bytes % 16 != 0) return FHOB_ERR_SHAPE;  // rows must stay 16-byte aligned
-  if (p->d > 128) return FHOB_ERR_SHAPE;
+  const size_t es = p->dtype == FHOB_F32 ? 4 : 2;
+  const int dv = head_dim_v(*p);
+  if ((p->d * es) % 16 != 0 || (dv * es) % 16 != 0) return FHOB_ERR_SHAPE;  // rows must stay 16-byte aligned
+  if (p->d > 128 || dv > 128) return FHOB_ERR_SHAPE;
   if (!p->workspace || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) return FHOB_ERR_WORKSPACE;
   if (p->workspace_bytes < fhob_workspace_bytes(p->bh, p->n_q)) return FHOB_ERR_WORKSPACE;
   if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) return FHOB_ERR_SHAPE;
@@ -152,8 +153,8 @@ const char* fhob_strerror(int status) {
   switch (status) {
     case FHOB_OK: return "ok";
     case FHOB_ERR_ARG: return "invalid argument (null pointer, bad dtype/impl/causal flag or non-positive size)";
-    case FHOB_ERR_SHAPE: return "shape not supported (head dim must keep rows 16-byte aligned and be <= 128; "
-                                "the tensor-core kernels need bf16 and d in {64,128})";
+    case FHOB_ERR_SHAPE: return "shape not supported (head dims must keep rows 16-byte aligned and be <= 128; "
+                                "the tensor-core kernels need 16-bit elements and head dims in {64,128})";
     case FHOB_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
     case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes()";
     case FHOB_ERR_CUDA: return "a CUDA call failed (see fhob_last_cuda_error)";
@@ -188,15 +189,15 @@ static int run_prepass(const FhobProblem* p, void* stream) {
   if (p->dtype == FHOB_BF16) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
-        rv.status, rows, p->d, p->n_q, first_live);
+        rv.status, rows, head_dim_v(*p), p->n_q, first_live);
   } else if (p->dtype == FHOB_F16) {
     prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
                                                        static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                       rv.status, rows, p->d, p->n_q, first_live);
+                                                       rv.status, rows, head_dim_v(*p), p->n_q, first_live);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                      rv.status, rows, p->d, p->n_q, first_live);
+                                                      rv.status, rows, head_dim_v(*p), p->n_q, first_live);
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
@@ -288,7 +289,8 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
 
 int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream) {
   if (!p || !p->q || !p->k || !p->v || !lse_out) return FHOB_ERR_ARG;
-  if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128) return FHOB_ERR_SHAPE;
+  if (p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0 || p->d <= 0 || p->d > 128 || p->d_v < 0 || p->d_v > 128)
+    return FHOB_ERR_SHAPE;
   if (p->dtype != FHOB_BF16 && p->dtype != FHOB_F32 && p->dtype != FHOB_F16) return FHOB_ERR_ARG;
   if (p->window < 0 || (p->window > 0 && p->causal != 1)) return FHOB_ERR_ARG;
   if (p->impl != FHOB_IMPL_AUTO && p->impl != FHOB_IMPL_SIMT && p->impl != FHOB_IMPL_TCGEN05) return FHOB_ERR_ARG;

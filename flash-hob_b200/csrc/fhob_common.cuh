@@ -38,6 +38,9 @@ struct RowVectors {
   float* k23;   // -D*dd - b
 };
 
+// Head dim of V, ddV, dO, O and of the results ddO, dV2 (0 in the struct = same as d).
+inline int head_dim_v(const FhobProblem& p) { return p.d_v > 0 ? p.d_v : p.d; }
+
 // Entries per head of a row vector: n_q rounded up to a multiple of four, so that every head's
 // slice (and every 64-query group the key-tiled kernels fetch with a bulk copy) starts on a
 // 16-byte boundary whatever n_q is.

@@ -9,8 +9,11 @@
 // score-shaped tiles S, A2, dP, X from fp32 dot products, applies the
 // elementwise formulas of fhob_common.cuh and either reduces along the row
 // (passes 1, 2) or feeds the resulting tiles into the output products
-// (passes 3, 4).  Arbitrary n_q, n_k and d <= 128 are handled by bounds checks;
-// pairs outside the matrix or hidden by the causal mask contribute zero.
+// (passes 3, 4).  Arbitrary n_q, n_k and head dims <= 128 are handled by bounds
+// checks; pairs outside the matrix or hidden by the causal mask contribute zero.
+// Two head dims: Q, K, ddQ, ddK, dQ2, dK2 have `d` columns, V, ddV, dO, O, ddO, dV2
+// have `dv` (jax_refs/flash_impl.py:381-389 has d_in != d_out); shared-memory
+// tiles all use the row pitch of the larger one.
 #include "fhob_common.cuh"
 
 namespace fhob {
@@ -27,7 +30,7 @@ struct SimtParams {
   void *dq2, *dk2, *dv2, *ddo;
   const float *nlc, *k1;
   float *ndd, *k23;
-  int n_q, n_k, d, causal, window;
+  int n_q, n_k, d, dv, causal, window;
   float scale;
 };
 
@@ -87,8 +90,8 @@ __device__ __forceinline__ float warp_max(float x) {
 template <typename T, int PASS>
 __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   extern __shared__ float smem[];
-  const int d = p.d;
-  const int ld = d + 1;
+  const int d = p.d, dv = p.dv;
+  const int ld = (d > dv ? d : dv) + 1;
   constexpr bool kQStationary = PASS != 4;
   float* stat[4];
   float* strm[4];
@@ -102,8 +105,8 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * TM;
   const int bh = blockIdx.y;
-  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
-  const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
+  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
+  const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);  // row-vector offset
   const int causal_off = p.n_k - p.n_q;
   const int n_stat = kQStationary ? p.n_q : p.n_k;
@@ -112,12 +115,12 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   if (kQStationary) {
     load_tile<T>(stat[0], ld, p.q, qoff, m0, TM, p.n_q, d);
     load_tile<T>(stat[1], ld, p.ddq, qoff, m0, TM, p.n_q, d);
-    if (PASS >= 2) load_tile<T>(stat[2], ld, p.d_o, qoff, m0, TM, p.n_q, d);
+    if (PASS >= 2) load_tile<T>(stat[2], ld, p.d_o, qoff_v, m0, TM, p.n_q, dv);
   } else {
     load_tile<T>(stat[0], ld, p.k, koff, m0, TM, p.n_k, d);
     load_tile<T>(stat[1], ld, p.ddk, koff, m0, TM, p.n_k, d);
-    load_tile<T>(stat[2], ld, p.v, koff, m0, TM, p.n_k, d);
-    load_tile<T>(stat[3], ld, p.ddv, koff, m0, TM, p.n_k, d);
+    load_tile<T>(stat[2], ld, p.v, koff_v, m0, TM, p.n_k, dv);
+    load_tile<T>(stat[3], ld, p.ddv, koff_v, m0, TM, p.n_k, dv);
   }
 
   // per-row constants of the stationary queries (passes 1-3)
@@ -152,13 +155,13 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
       load_tile<T>(strm[0], ld, p.k, koff, n0, TN, p.n_k, d);
       load_tile<T>(strm[1], ld, p.ddk, koff, n0, TN, p.n_k, d);
       if (PASS >= 2) {
-        load_tile<T>(strm[2], ld, p.v, koff, n0, TN, p.n_k, d);
-        load_tile<T>(strm[3], ld, p.ddv, koff, n0, TN, p.n_k, d);
+        load_tile<T>(strm[2], ld, p.v, koff_v, n0, TN, p.n_k, dv);
+        load_tile<T>(strm[3], ld, p.ddv, koff_v, n0, TN, p.n_k, dv);
       }
     } else {
       load_tile<T>(strm[0], ld, p.q, qoff, n0, TN, p.n_q, d);
       load_tile<T>(strm[1], ld, p.ddq, qoff, n0, TN, p.n_q, d);
-      load_tile<T>(strm[2], ld, p.d_o, qoff, n0, TN, p.n_q, d);
+      load_tile<T>(strm[2], ld, p.d_o, qoff_v, n0, TN, p.n_q, dv);
       if (threadIdx.x < TN) {
         int qi = n0 + threadIdx.x;
         bool ok = qi < p.n_q;
@@ -175,20 +178,23 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
     float s[RPW], a2[RPW], dp[RPW], x[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) s[i] = a2[i] = dp[i] = x[i] = 0.f;
-    for (int e = 0; e < d; ++e) {
+    for (int e = 0; e < d; ++e) {   // contractions over the q/k head dim
       float c0 = strm[0][lane * ld + e], c1 = strm[1][lane * ld + e];
-      float c2 = 0.f, c3 = 0.f;
-      if (PASS >= 2) {
-        c2 = strm[2][lane * ld + e];
-        if (kQStationary) c3 = strm[3][lane * ld + e];
-      }
 #pragma unroll
       for (int i = 0; i < RPW; ++i) {
         int r = warp * RPW + i;
         float a0 = stat[0][r * ld + e], a1 = stat[1][r * ld + e];
         s[i] = fmaf(a0, c0, s[i]);
         a2[i] = fmaf(a1, c0, fmaf(a0, c1, a2[i]));
-        if (PASS >= 2) {
+      }
+    }
+    if (PASS >= 2) {
+      for (int e = 0; e < dv; ++e) {   // contractions over the v head dim
+        float c2 = strm[2][lane * ld + e];
+        float c3 = kQStationary ? strm[3][lane * ld + e] : 0.f;
+#pragma unroll
+        for (int i = 0; i < RPW; ++i) {
+          int r = warp * RPW + i;
           float a2v = stat[2][r * ld + e];
           dp[i] = fmaf(a2v, c2, dp[i]);
           if (kQStationary) x[i] = fmaf(a2v, c3, x[i]);
@@ -237,11 +243,11 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
 #pragma unroll
         for (int m = 0; m < DCH; ++m) {
           int col = lane + 32 * m;
-          bool in = col < d;
+          bool in = col < d, in_v = col < dv;
           bds[m] = in ? b_ds[c * ld + col] : 0.f;
           bds2[m] = in ? b_ds2[c * ld + col] : 0.f;
-          bddp[m] = in ? b_ddp[c * ld + col] : 0.f;
-          bp[m] = (in && kQStationary) ? strm[3][c * ld + col] : 0.f;
+          bddp[m] = in_v ? b_ddp[c * ld + col] : 0.f;
+          bp[m] = (in_v && kQStationary) ? strm[3][c * ld + col] : 0.f;
         }
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
@@ -273,7 +279,7 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
   } else {
     void* o0 = kQStationary ? p.dq2 : p.dk2;
     void* o1 = kQStationary ? p.ddo : p.dv2;
-    size_t off = kQStationary ? qoff : koff;
+    size_t off = kQStationary ? qoff : koff, off_v = kQStationary ? qoff_v : koff_v;
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
       int gr = m0 + warp * RPW + i;
@@ -281,10 +287,8 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
 #pragma unroll
       for (int m = 0; m < DCH; ++m) {
         int col = lane + 32 * m;
-        if (col < d) {
-          st_elem<T>(o0, off + static_cast<size_t>(gr) * d + col, out0[i][m]);
-          st_elem<T>(o1, off + static_cast<size_t>(gr) * d + col, out1[i][m]);
-        }
+        if (col < d) st_elem<T>(o0, off + static_cast<size_t>(gr) * d + col, out0[i][m]);
+        if (col < dv) st_elem<T>(o1, off_v + static_cast<size_t>(gr) * dv + col, out1[i][m]);
       }
     }
   }
@@ -294,7 +298,7 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
 template <typename T>
 __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, void* o_out, float* lse_out) {
   extern __shared__ float smem[];
-  const int d = p.d, ld = d + 1;
+  const int d = p.d, dv = p.dv, ld = (d > dv ? d : dv) + 1;
   float* qs = smem;
   float* ks = qs + TM * ld;
   float* vs = ks + TN * ld;
@@ -302,8 +306,8 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
   constexpr int LT = TN + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * TM, bh = blockIdx.y;
-  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
-  const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
+  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
+  const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const int causal_off = p.n_k - p.n_q;
   load_tile<T>(qs, ld, p.q, qoff, m0, TM, p.n_q, d);
   float mrow[RPW], lrow[RPW], acc[RPW][DCH];
@@ -321,7 +325,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
     const int n0 = t * TN;
     __syncthreads();
     load_tile<T>(ks, ld, p.k, koff, n0, TN, p.n_k, d);
-    load_tile<T>(vs, ld, p.v, koff, n0, TN, p.n_k, d);
+    if (o_out) load_tile<T>(vs, ld, p.v, koff_v, n0, TN, p.n_k, dv);
     __syncthreads();
     float s[RPW];
 #pragma unroll
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 #pragma unroll
       for (int m = 0; m < DCH; ++m) {
         int col = lane + 32 * m;
-        bv[m] = col < d ? vs[c * ld + col] : 0.f;
+        bv[m] = (col < dv && o_out) ? vs[c * ld + col] : 0.f;
       }
 #pragma unroll
       for (int i = 0; i < RPW; ++i) {
@@ -369,7 +373,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 #pragma unroll
     for (int m = 0; m < DCH; ++m) {
       int col = lane + 32 * m;
-      if (col < d && o_out) st_elem<T>(o_out, qoff + static_cast<size_t>(qi) * d + col, acc[i][m] * inv);
+      if (col < dv && o_out) st_elem<T>(o_out, qoff_v + static_cast<size_t>(qi) * dv + col, acc[i][m] * inv);
     }
     if (lane == 0)
       lse_out[static_cast<size_t>(bh) * p.n_q + qi] =
@@ -384,7 +388,7 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
 template <typename T, bool KSIDE>
 __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, void* out0, void* out1) {
   extern __shared__ float smem[];
-  const int d = p.d, ld = d + 1;
+  const int d = p.d, dv = p.dv, ld = (d > dv ? d : dv) + 1;
   float* stat0 = smem;                       // Q | K
   float* stat1 = stat0 + TM * ld;            // dO | V
   float* strm0 = stat1 + TM * ld;            // K | Q
@@ -394,17 +398,17 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
   constexpr int LT = TN + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * TM, bh = blockIdx.y;
-  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d;
-  const size_t koff = static_cast<size_t>(bh) * p.n_k * d;
+  const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
+  const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);
   const int causal_off = p.n_k - p.n_q;
   const int n_stat = KSIDE ? p.n_k : p.n_q, n_strm = KSIDE ? p.n_q : p.n_k;
   if (KSIDE) {
     load_tile<T>(stat0, ld, p.k, koff, m0, TM, p.n_k, d);
-    load_tile<T>(stat1, ld, p.v, koff, m0, TM, p.n_k, d);
+    load_tile<T>(stat1, ld, p.v, koff_v, m0, TM, p.n_k, dv);
   } else {
     load_tile<T>(stat0, ld, p.q, qoff, m0, TM, p.n_q, d);
-    load_tile<T>(stat1, ld, p.d_o, qoff, m0, TM, p.n_q, d);
+    load_tile<T>(stat1, ld, p.d_o, qoff_v, m0, TM, p.n_q, dv);
   }
   float r_nlc[RPW], r_k1[RPW];
 #pragma unroll
@@ -427,7 +431,7 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
     __syncthreads();
     if (KSIDE) {
       load_tile<T>(strm0, ld, p.q, qoff, n0, TN, p.n_q, d);
-      load_tile<T>(strm1, ld, p.d_o, qoff, n0, TN, p.n_q, d);
+      load_tile<T>(strm1, ld, p.d_o, qoff_v, n0, TN, p.n_q, dv);
       if (threadIdx.x < TN) {
         const int qi = n0 + threadIdx.x;
         svec[threadIdx.x] = qi < p.n_q ? p.nlc[voff + qi] : 0.f;
@@ -435,20 +439,21 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
       }
     } else {
       load_tile<T>(strm0, ld, p.k, koff, n0, TN, p.n_k, d);
-      load_tile<T>(strm1, ld, p.v, koff, n0, TN, p.n_k, d);
+      load_tile<T>(strm1, ld, p.v, koff_v, n0, TN, p.n_k, dv);
     }
     __syncthreads();
     float s[RPW], dp[RPW];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) s[i] = dp[i] = 0.f;
     for (int e = 0; e < d; ++e) {
-      const float c0 = strm0[lane * ld + e], c1 = strm1[lane * ld + e];
+      const float c0 = strm0[lane * ld + e];
 #pragma unroll
-      for (int i = 0; i < RPW; ++i) {
-        const int r = warp * RPW + i;
-        s[i] = fmaf(stat0[r * ld + e], c0, s[i]);
-        dp[i] = fmaf(stat1[r * ld + e], c1, dp[i]);
-      }
+      for (int i = 0; i < RPW; ++i) s[i] = fmaf(stat0[(warp * RPW + i) * ld + e], c0, s[i]);
+    }
+    for (int e = 0; e < dv; ++e) {
+      const float c1 = strm1[lane * ld + e];
+#pragma unroll
+      for (int i = 0; i < RPW; ++i) dp[i] = fmaf(stat1[(warp * RPW + i) * ld + e], c1, dp[i]);
     }
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
@@ -466,8 +471,8 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
 #pragma unroll
       for (int m = 0; m < DCH; ++m) {
         const int col = lane + 32 * m;
-        b0[m] = col < d ? strm0[c * ld + col] : 0.f;   // K | Q
-        b1[m] = col < d ? strm1[c * ld + col] : 0.f;   // V | dO
+        b0[m] = col < d ? strm0[c * ld + col] : 0.f;    // K | Q
+        b1[m] = col < dv ? strm1[c * ld + col] : 0.f;   // V | dO
       }
 #pragma unroll
       for (int i = 0; i < RPW; ++i) {
@@ -489,17 +494,20 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
 #pragma unroll
     for (int m = 0; m < DCH; ++m) {
       const int col = lane + 32 * m;
-      if (col < d) {
-        st_elem<T>(out0, off + static_cast<size_t>(gr) * d + col, acc0[i][m]);
-        if (KSIDE) st_elem<T>(out1, off + static_cast<size_t>(gr) * d + col, acc1[i][m]);
-      }
+      if (col < d) st_elem<T>(out0, off + static_cast<size_t>(gr) * d + col, acc0[i][m]);
+      if (KSIDE && col < dv) st_elem<T>(out1, koff_v + static_cast<size_t>(gr) * dv + col, acc1[i][m]);
     }
   }
 }
 
 
-size_t pass_smem_bytes(int d) {
-  size_t ld = d + 1;
+int pitch(const FhobProblem& p) {  // row pitch of the shared-memory tiles: the larger head dim + 1
+  const int dv = head_dim_v(p);
+  return (p.d > dv ? p.d : dv) + 1;
+}
+
+size_t pass_smem_bytes(const FhobProblem& p) {
+  size_t ld = pitch(p);
   return sizeof(float) * ((4 * TM + 4 * TN) * ld + 8 * TM * (TN + 1) + 4 * TN);
 }
 
@@ -509,13 +517,13 @@ SimtParams make_params(const FhobProblem& p) {
   s.q = p.q; s.k = p.k; s.v = p.v; s.d_o = p.d_o; s.ddq = p.ddq; s.ddk = p.ddk; s.ddv = p.ddv;
   s.dq2 = p.dq2; s.dk2 = p.dk2; s.dv2 = p.dv2; s.ddo = p.ddo;
   s.nlc = rv.nlc; s.k1 = rv.k1; s.ndd = rv.ndd; s.k23 = rv.k23;
-  s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.causal = p.causal; s.window = p.window; s.scale = p.scale;
+  s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.dv = head_dim_v(p); s.causal = p.causal; s.window = p.window; s.scale = p.scale;
   return s;
 }
 
 template <typename T, int PASS>
 int launch_pass(const FhobProblem& p, cudaStream_t st) {
-  size_t smem = pass_smem_bytes(p.d);
+  size_t smem = pass_smem_bytes(p);
   FHOB_CUDA_OK(cudaFuncSetAttribute(simt_pass_kernel<T, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem)));
   int n_stat = PASS == 4 ? p.n_k : p.n_q;
@@ -538,7 +546,7 @@ int dispatch_pass(int pass, const FhobProblem& p, cudaStream_t st) {
 
 template <typename T>
 int launch_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t st) {
-  const size_t smem = sizeof(float) * ((2 * TM + 2 * TN) * (p.d + 1) + 2 * TM * (TN + 1) + 2 * TN);
+  const size_t smem = sizeof(float) * ((2 * TM + 2 * TN) * pitch(p) + 2 * TM * (TN + 1) + 2 * TN);
   SimtParams s = make_params(p);
   FHOB_CUDA_OK(cudaFuncSetAttribute(simt_backward_kernel<T, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem)));
@@ -554,22 +562,22 @@ int launch_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStre
 }  // namespace
 
 int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t st) {
-  if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
+  if (p.d > 32 * DCH || head_dim_v(p) > 32 * DCH) return FHOB_ERR_SHAPE;
   if (p.dtype == FHOB_F32) return launch_backward<float>(p, dq, dk, dv, st);
   if (p.dtype == FHOB_F16) return launch_backward<__half>(p, dq, dk, dv, st);
   return launch_backward<__nv_bfloat16>(p, dq, dk, dv, st);
 }
 
 int simt_pass(int pass, const FhobProblem& p, cudaStream_t st) {
-  if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
+  if (p.d > 32 * DCH || head_dim_v(p) > 32 * DCH) return FHOB_ERR_SHAPE;
   if (p.dtype == FHOB_F32) return dispatch_pass<float>(pass, p, st);
   if (p.dtype == FHOB_F16) return dispatch_pass<__half>(pass, p, st);
   return dispatch_pass<__nv_bfloat16>(pass, p, st);
 }
 
 int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t st) {
-  if (p.d > 32 * DCH) return FHOB_ERR_SHAPE;
-  size_t smem = sizeof(float) * ((TM + 2 * TN) * (p.d + 1) + TM * (TN + 1));
+  if (p.d > 32 * DCH || head_dim_v(p) > 32 * DCH) return FHOB_ERR_SHAPE;
+  size_t smem = sizeof(float) * ((TM + 2 * TN) * pitch(p) + TM * (TN + 1));
   dim3 grid((p.n_q + TM - 1) / TM, p.bh);
   SimtParams s = make_params(p);
   if (p.dtype == FHOB_F32) {

@@ -73,9 +73,10 @@ __device__ __forceinline__ void gemm_ss(bool leader, uint32_t d_tmem, uint32_t a
 }
 
 // D (+)= A . B with A = bf16 tile in TMEM (128 x BN, 8 columns per 16 rows of B) and B = streamed
-// tile (BN rows x D) read MN-major: the contraction runs down the BN rows, 2048 bytes per step.
-// b_lo must carry the leading byte offset (distance between the two 64-column boxes).
-template <int D, int BN>
+// tile (BN rows x N columns, N in idesc) read MN-major: the contraction runs down the BN rows,
+// 2048 bytes per step.  b_lo must carry the leading byte offset (distance between the tile's two
+// 64-column boxes; not used when the tile has a single box).
+template <int BN>
 __device__ __forceinline__ void gemm_ts(bool leader, uint32_t d_tmem, uint32_t a_region, uint32_t b_lo,
                                         uint32_t idesc, bool accumulate) {
   constexpr int CH = BN / 32;
@@ -111,7 +112,7 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (bh, n, d) bf16 row-major tensor, box = 64 columns x `rows` rows of one head, 128-byte swizzle.
+// (bh, n, d) 16-bit row-major tensor, box = 64 columns x `rows` rows of one head, 128-byte swizzle.
 int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, bool f16) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) {

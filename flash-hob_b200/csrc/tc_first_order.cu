@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             ok = wait_all(&bars->p_full[stage], (it >> 1) & 1) && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
             if (!ok) break;
             tc_fence_after();
-            gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, it > 0);  // O += P . V
+            gemm_ts<BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, it > 0);  // O += P . V
             commit(&bars->strm_free[slot]);
             if (MODE == FO_ONE) commit(&bars->o_done);
             if (leader) mbar_arrive(&bars->go[stage]);
@@ -277,13 +277,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             const uint32_t sl = strm_lo + slot * kSlot16;
             const bool accum = it > 0;
             if (MODE == FO_ONE) {
-              gemm_ts<D, BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
+              gemm_ts<BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
               commit(&bars->o_done);
             } else if (MODE == FO_BQ) {
-              gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
+              gemm_ts<BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
             } else {
-              gemm_ts<D, BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
-              gemm_ts<D, BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
+              gemm_ts<BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
+              gemm_ts<BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
             }
             commit(&bars->strm_free[slot]);
             if (C::NACC == 2 && leader) mbar_arrive(&bars->go[stage]);
@@ -665,7 +665,8 @@ int tc_selftest_expired_wait(int* status, cudaStream_t s) {
   return FHOB_OK;
 }
 
-bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p); }
+// the first-order kernels take one head dim; problems with d_v != d run on the CUDA-core kernels
+bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p) && head_dim_v(p) == p.d; }
 
 int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;

@@ -34,6 +34,8 @@
 //   computes group B; while they turn group B into dS / dS2, it runs the group-A outputs and
 //   group A of the next tile.  The bf16 tiles overwrite their own accumulators in place.
 // Every mbarrier wait is bounded: when it runs out the CTA raises the status word, drains and exits.
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 // pass 3: start the first elementwise half when S alone is complete (see ew_half_a)
@@ -45,38 +47,52 @@ namespace fhob {
 namespace {
 
 
-template <int PASS, int D, int BN>
+template <int PASS, int DQK, int DV, int BN>
 struct Cfg {
   static constexpr int NSTAT = PASS == 1 ? 2 : (PASS == 4 ? 4 : 3);
   static constexpr int NSTRM = PASS == 1 ? 2 : (PASS == 4 ? 3 : 4);
   static constexpr int NACC = PASS == 1 ? 2 : 4;
   static constexpr int NOUT = PASS >= 3 ? 2 : 0;
-  static constexpr int OUT_COLS = NOUT * D;
+  // Two head dims (jax_refs/flash_impl.py:381-389 uses d_in != d_out): Q, K, ddQ, ddK and the
+  // results dQ2, dK2 have DQK columns; V, ddV, dO and the results ddO, dV2 have DV columns.  In
+  // every pass the first two stationary and the first two streamed tiles are of the first kind
+  // (passes 1-3: Q, ddQ | dO and K, ddK | V, ddV; pass 4: K, ddK | V, ddV and Q, ddQ | dO).
+  __host__ __device__ static constexpr int tile_d(int i) { return i < 2 ? DQK : DV; }
+  static constexpr int OUT0_COLS = NOUT ? DQK : 0;   // dQ2 | dK2
+  static constexpr int OUT1_COLS = NOUT ? DV : 0;    // ddO | dV2
+  static constexpr int OUT_COLS = OUT0_COLS + OUT1_COLS;
   static constexpr int STAGE_COLS = NACC * BN;
   // score stages in TMEM: two for the reducing passes, one (pipelined in halves) for passes 3, 4
   static constexpr int NSS = PASS <= 2 ? ((TMEM_COLS - OUT_COLS) / STAGE_COLS >= 2 ? 2 : 1) : 1;
-  static constexpr int STAT_BYTES = BM * D * 2;
-  static constexpr int STRM_BYTES = BN * D * 2;
-  // pass 4: the four per-query constant vectors of the streamed queries travel with the slot
-  static constexpr int STATS_BYTES = PASS == 4 ? 4 * BN * 4 : 0;
-  static constexpr int SLOT_BYTES = NSTRM * STRM_BYTES + STATS_BYTES;
-  static constexpr int NSLOT_FIT = (SMEM_LIMIT - SMEM_TAIL - NSTAT * STAT_BYTES) / SLOT_BYTES;
-  static constexpr int NSLOT = NSLOT_FIT > 4 ? 4 : NSLOT_FIT;
-  static constexpr int SMEM_BYTES = NSTAT * STAT_BYTES + NSLOT * SLOT_BYTES + SMEM_TAIL;
-  // Streamed tiles 2p and 2p+1 form a pair whose 64-column boxes interleave in shared memory
-  // (box b of tile 2p, box b of tile 2p+1, box b+1 of tile 2p, ...), so that one K-major operand
-  // descriptor can cover both tiles stacked as 2*BN rows: products that share their A operand
-  // (S and Q.ddK^T; dP and X) are then issued as one MMA with N = 2*BN.  A tcgen05.mma occupies
-  // the tensor pipe for max(N/2, ~50) cycles on B200 (measured), so two N = 64 products cost 104
-  // cycles where one N = 128 product costs 64.  An unpaired last tile keeps the compact layout.
+  __host__ __device__ static constexpr int stat_bytes(int i) { return BM * tile_d(i) * 2; }
+  __host__ __device__ static constexpr int strm_bytes(int i) { return BN * tile_d(i) * 2; }
+  __host__ __device__ static constexpr int stat_off(int i) { return i == 0 ? 0 : stat_off(i - 1) + stat_bytes(i - 1); }
+  static constexpr int STAT_BYTES = stat_off(NSTAT);
+  // Streamed tiles 2p and 2p+1 form a pair (same head dim) whose 64-column boxes interleave in
+  // shared memory (box b of tile 2p, box b of tile 2p+1, box b+1 of tile 2p, ...), so that one
+  // K-major operand descriptor can cover both tiles stacked as 2*BN rows: products that share
+  // their A operand (S and Q.ddK^T; dP and X) are then issued as one MMA with N = 2*BN.  A
+  // tcgen05.mma occupies the tensor pipe for max(N/2, ~50) cycles on B200 (measured), so two
+  // N = 64 products cost 104 cycles where one N = 128 product costs 64.  An unpaired last tile
+  // keeps the compact layout.
   __host__ __device__ static constexpr bool paired(int i) { return (i / 2) * 2 + 1 < NSTRM; }
+  __host__ __device__ static constexpr int pair_off(int pr) {  // byte offset of the pair's first box
+    return pr == 0 ? 0 : pair_off(pr - 1) + strm_bytes(2 * (pr - 1)) * (paired(2 * (pr - 1)) ? 2 : 1);
+  }
   __host__ __device__ static constexpr int strm_base(int i) {
-    return (i / 2) * 2 * STRM_BYTES + (paired(i) ? (i % 2) * BN * 128 : 0);
+    return pair_off(i / 2) + (paired(i) ? (i % 2) * BN * 128 : 0);
   }
   __host__ __device__ static constexpr int strm_box(int i) { return paired(i) ? 2 * BN * 128 : BN * 128; }
+  static constexpr int STRM_BYTES = pair_off((NSTRM + 1) / 2);   // all streamed tiles of a slot
+  // pass 4: the four per-query constant vectors of the streamed queries travel with the slot
+  static constexpr int STATS_BYTES = PASS == 4 ? 4 * BN * 4 : 0;
+  static constexpr int SLOT_BYTES = STRM_BYTES + STATS_BYTES;
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - SMEM_TAIL - STAT_BYTES) / SLOT_BYTES;
+  static constexpr int NSLOT = NSLOT_FIT > 4 ? 4 : NSLOT_FIT;
+  static constexpr int SMEM_BYTES = STAT_BYTES + NSLOT * SLOT_BYTES + SMEM_TAIL;
   static_assert(NSS * STAGE_COLS + OUT_COLS <= TMEM_COLS, "TMEM budget");
   static_assert(NSLOT >= 2, "need two streamed slots");
-  static_assert(D == 64 || D == 128, "head dim");
+  static_assert((DQK == 64 || DQK == 128) && (DV == 64 || DV == 128), "head dims");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 128, "streamed tile");
   static_assert(PASS <= 2 || BN == 64, "passes 3 and 4 are written for 64-row streamed tiles");
 };
@@ -305,17 +321,17 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
   tmem_st16(acc + 3 * BN, w_ds2);
 }
 
-template <int PASS, int D, int BN, int FUSED = 0, bool F16 = false>
+template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
   static_assert(FUSED == 0 || PASS == 2, "only pass 2 has a fused form");
-  using C = Cfg<PASS, D, BN>;
+  using C = Cfg<PASS, DQK, DV, BN>;
   constexpr bool kQStat = PASS != 4;
   // passes 1, 2: a third warp issues the second product of group A (their tensor pipe has the room;
   // in passes 3, 4 the extra issuer only delayed group A)
   constexpr bool kThirdIssuer = PASS <= 2;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stat_tiles = smem;
-  uint8_t* strm_tiles = smem + C::NSTAT * C::STAT_BYTES;
+  uint8_t* strm_tiles = smem + C::STAT_BYTES;
   Bars* bars = reinterpret_cast<Bars*>(strm_tiles + C::NSLOT * C::SLOT_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -377,10 +393,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
   if (warp == TMA_WARP) {
     // ================================================= TMA producer
     if (lane == 0 && n_iter > 0) {
-      mbar_arrive_expect_tx(&bars->stat_full, C::NSTAT * C::STAT_BYTES);
+      mbar_arrive_expect_tx(&bars->stat_full, C::STAT_BYTES);
+#pragma unroll
       for (int i = 0; i < C::NSTAT; ++i)
-        for (int bx = 0; bx < D / 64; ++bx)
-          tma_load_3d(stat_tiles + i * C::STAT_BYTES + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
+        for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
+          tma_load_3d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
                       head);
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
@@ -389,13 +406,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         mbar_arrive_expect_tx(&bars->strm_full[slot], C::SLOT_BYTES);
         uint8_t* dst = strm_tiles + slot * C::SLOT_BYTES;
         const int n0 = (t_begin + it) * BN;
+#pragma unroll
         for (int i = 0; i < C::NSTRM; ++i)
-          for (int bx = 0; bx < D / 64; ++bx)
+          for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
             tma_load_3d(dst + C::strm_base(i) + bx * C::strm_box(i), &p.strm[i], &bars->strm_full[slot], bx * 64,
                         n0, head);
         if (PASS == 4) {
           const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
-          uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
+          uint8_t* sv = dst + C::STRM_BYTES;
           bulk_load(sv + 0 * BN * 4, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
           bulk_load(sv + 1 * BN * 4, p.ndd + vo, BN * 4, &bars->strm_full[slot]);
           bulk_load(sv + 2 * BN * 4, p.k1 + vo, BN * 4, &bars->strm_full[slot]);
@@ -432,13 +450,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       };
       constexpr uint32_t idesc_s1 = umma_idesc_bf16(BM, BN, false, false, F16);      // one streamed tile
       constexpr uint32_t idesc_s2 = umma_idesc_bf16(BM, 2 * BN, false, false, F16);  // a stacked pair
-      constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true, F16);
+      constexpr uint32_t idesc_o0 = umma_idesc_bf16(BM, DQK, false, true, F16);  // dQ2 | dK2
+      constexpr uint32_t idesc_o1 = umma_idesc_bf16(BM, DV, false, true, F16);   // ddO | dV2
       constexpr int kStatBox = BM * 128;
       // low descriptor words of the tiles: K-major use (LBO field unused, set to 1) and MN-major
       // use of streamed tile i (LBO = distance between its two 64-column boxes)
       const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
       const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
-      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4;
+      constexpr uint32_t kSlot16 = C::SLOT_BYTES >> 4;
+      auto stat_i = [&](int i) { return stat_lo + (C::stat_off(i) >> 4); };
       auto k_lo = [&](uint32_t slot_lo, int i) { return slot_lo + (C::strm_base(i) >> 4); };
       auto mn_lo = [&](uint32_t slot_lo, int i) {
         return slot_lo - (1u << 16) + (C::strm_base(i) >> 4) + (static_cast<uint32_t>(C::strm_box(i) >> 4) << 16);
@@ -454,20 +474,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         tc_fence_after();
         const uint32_t sl = strm_lo + slot * kSlot16;
         if (chain == 0) {
-          gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
+          gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
           if (kThirdIssuer) {
             // A2 += stat1 . strm0^T is issued by the third warp, strictly behind the stacked product
             // so that the order of the fp32 accumulation (and with it every result bit) is fixed
             if (leader) mbar_arrive(&bars->a2_go);
           } else {
             if (early_s(PASS)) commit(&bars->s_ready);
-            gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16, k_lo(sl, 0), idesc_s1, true);
+            gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_i(1), k_lo(sl, 0), idesc_s1, true);
           }
         } else if (PASS == 4) {
-          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s1, false);
-          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_lo + 3 * kStat16, k_lo(sl, 2), idesc_s1, false);
+          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s1, false);
+          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_i(3), k_lo(sl, 2), idesc_s1, false);
         } else {
-          gemm_ss<D, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_lo + 2 * kStat16, k_lo(sl, 2), idesc_s2, false);
+          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s2, false);
         }
         return true;
       };
@@ -487,7 +507,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         // scores(t+1) ...  The bf16 tiles sit where the chain's own accumulators were, and its
         // MMAs execute in issue order, so scores(t+1) cannot overtake outputs(t).
         const uint32_t acc = tmem_base + C::OUT_COLS;
-        const uint32_t out0 = tmem_base, out1 = tmem_base + D;
+        const uint32_t out0 = tmem_base, out1 = tmem_base + C::OUT0_COLS;
         ok = ok && issue_scores(0, acc);
         if (ok) commit(&bars->s_full[chain]);
         for (int it = 0; ok && it < n_iter; ++it) {
@@ -497,11 +517,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           if (!ok) break;
           tc_fence_after();
           if (chain == 0) {
-            gemm_ts<D, BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o, accum);              // ddP . V | dO
-            if (kQStat) gemm_ts<D, BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o, true);   // P . ddV
+            gemm_ts<BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o1, accum);              // ddP . V | dO
+            if (kQStat) gemm_ts<BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o1, true);   // P . ddV
           } else {
-            gemm_ts<D, BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o, accum);  // dS  . ddK | ddQ
-            gemm_ts<D, BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o, true);   // dS2 . K   | Q
+            gemm_ts<BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o0, accum);  // dS  . ddK | ddQ
+            gemm_ts<BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o0, true);   // dS2 . K   | Q
           }
           commit(&bars->strm_free[it % C::NSLOT]);
           // Chain 1's group A of the next tile gates the next elementwise half, while chain 2's
@@ -541,7 +561,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       constexpr int kStatBox = BM * 128;
       const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
       const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
-      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4;
+      constexpr uint32_t kSlot16 = C::SLOT_BYTES >> 4;
       bool ok = wait_all(&bars->stat_full, 0);
       for (int it = 0; ok && it < n_iter; ++it) {
         const int slot = it % C::NSLOT;
@@ -551,8 +571,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + C::OUT_COLS + (PASS <= 2 ? stage * C::STAGE_COLS : 0);
-        gemm_ss<D, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + kStat16,
-                                             strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
+        gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + (C::stat_off(1) >> 4),
+                                               strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
         if (leader) {
           umma_commit(&bars->s_full[stage]);
           umma_commit(&bars->strm_free[slot]);
@@ -633,7 +653,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           const int slot = it % C::NSLOT;
           ok = __all_sync(0xffffffffu, wait_bar(&bars->strm_full[slot], (it / C::NSLOT) & 1, bars, p.status));
           if (!ok) break;
-          c.sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::NSTRM * C::STRM_BYTES);
+          c.sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::STRM_BYTES);
         }
         ok = __all_sync(0xffffffffu, wait_bar(early_s(PASS) ? &bars->s_ready : &bars->s_full[0], it & 1, bars, p.status));
         if (!ok) break;
@@ -694,40 +714,33 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, p.status));
       tc_fence_after();
       if (ok) {
+        auto store_out = [&](auto width, uint32_t col0, uint16_t* base, float mul) {
+          constexpr int DO = decltype(width)::value;   // columns of this result
+          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * DO + half * (DO / 2);
 #pragma unroll
-        for (int o = 0; o < 2; ++o) {
-          uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
-                               (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
-#pragma unroll
-          for (int ch = 0; ch < D / 32; ++ch) {
+          for (int ch = 0; ch < DO / 32; ++ch) {
             uint32_t v[16];
             if (n_iter > 0) {
-              tmem_ld16(tmem_base + lane_base + o * D + half * (D / 2) + 16 * ch, v);
+              tmem_ld16(tmem_base + lane_base + col0 + half * (DO / 2) + 16 * ch, v);
               tmem_wait_ld();
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j) v[j] = 0u;
             }
-            if (o == 0) {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * c.scale);
-            }
             if (g_row < n_stat) {
-              uint4 w0, w1;
-              w0.x = pack16<F16>(__uint_as_float(v[0]), __uint_as_float(v[1]));
-              w0.y = pack16<F16>(__uint_as_float(v[2]), __uint_as_float(v[3]));
-              w0.z = pack16<F16>(__uint_as_float(v[4]), __uint_as_float(v[5]));
-              w0.w = pack16<F16>(__uint_as_float(v[6]), __uint_as_float(v[7]));
-              w1.x = pack16<F16>(__uint_as_float(v[8]), __uint_as_float(v[9]));
-              w1.y = pack16<F16>(__uint_as_float(v[10]), __uint_as_float(v[11]));
-              w1.z = pack16<F16>(__uint_as_float(v[12]), __uint_as_float(v[13]));
-              w1.w = pack16<F16>(__uint_as_float(v[14]), __uint_as_float(v[15]));
+              uint32_t w[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                w[j] = pack16<F16>(__uint_as_float(v[2 * j]) * mul, __uint_as_float(v[2 * j + 1]) * mul);
               uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
-              d4[0] = w0;
-              d4[1] = w1;
+              d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
-        }
+        };
+        // dS and dS2 were stored without the factor `scale`: it is applied to dQ2 | dK2 here
+        store_out(std::integral_constant<int, DQK>{}, 0, p.out0, c.scale);
+        store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
       }
     }
   }
@@ -743,10 +756,10 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
 // ------------------------------------------------------------------ host side
 
-template <int PASS, int D, int BN, int FUSED = 0, bool F16 = false>
+template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
-  using C = Cfg<PASS, D, BN>;
-  constexpr auto kernel = tc_pass_kernel<PASS, D, BN, FUSED, F16>;
+  using C = Cfg<PASS, DQK, DV, BN>;
+  constexpr auto kernel = tc_pass_kernel<PASS, DQK, DV, BN, FUSED, F16>;
   RowVectors rv = row_vectors(p);
   TcParams tp;
   memset(&tp, 0, sizeof(tp));
@@ -754,11 +767,15 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   const void* k_side[4] = {p.k, p.ddk, p.v, p.ddv};
   int st = FHOB_OK;
   if (PASS != 4) {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, D, BM, F16);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, D, BN, F16);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
+      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
+      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BN, F16);
   } else {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, D, BM, F16);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, BN, F16);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
+      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
+      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BN, F16);
   }
   if (st != FHOB_OK) return st;
   tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
@@ -776,24 +793,33 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   return FHOB_OK;
 }
 
-template <int D, bool F16>
+template <int DQK, int DV, bool F16>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
   switch (pass) {
-    // pass 1 streams 128-row tiles (the stacked [K ; ddK] operand reaches N = 256), the others 64
-    case 1: return launch<1, D, 128, 0, F16>(p, s);
-    case 2: return launch<2, D, 64, 0, F16>(p, s);
-    case 12: return launch<2, D, 64, 1, F16>(p, s);  // passes 1 and 2 in one sweep
-    case 13: return launch<2, D, 64, 2, F16>(p, s);  // the same, also producing D = sum P dP (no O given)
-    case 3: return launch<3, D, 64, 0, F16>(p, s);
-    case 4: return launch<4, D, 64, 0, F16>(p, s);
+    // pass 1 streams 128-row tiles (the stacked [K ; ddK] operand reaches N = 256), the others 64;
+    // it touches no tile of the second head dim
+    case 1: return launch<1, DQK, DQK, 128, 0, F16>(p, s);
+    case 2: return launch<2, DQK, DV, 64, 0, F16>(p, s);
+    case 12: return launch<2, DQK, DV, 64, 1, F16>(p, s);  // passes 1 and 2 in one sweep
+    case 13: return launch<2, DQK, DV, 64, 2, F16>(p, s);  // the same, also producing D = sum P dP (no O given)
+    case 3: return launch<3, DQK, DV, 64, 0, F16>(p, s);
+    case 4: return launch<4, DQK, DV, 64, 0, F16>(p, s);
   }
   return FHOB_ERR_ARG;
+}
+
+template <bool F16>
+int dispatch_dims(int pass, const FhobProblem& p, cudaStream_t s) {
+  const int dv = head_dim_v(p);
+  if (p.d == 64) return dv == 64 ? dispatch<64, 64, F16>(pass, p, s) : dispatch<64, 128, F16>(pass, p, s);
+  return dv == 64 ? dispatch<128, 64, F16>(pass, p, s) : dispatch<128, 128, F16>(pass, p, s);
 }
 
 }  // namespace
 
 bool tc_supported(const FhobProblem& p) {
-  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128);
+  const int dv = head_dim_v(p);
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (dv == 64 || dv == 128);
 }
 
 int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
@@ -807,8 +833,7 @@ int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
     if (major != 10) return FHOB_ERR_ARCH;
     checked_dev = dev;
   }
-  if (p.dtype == FHOB_F16) return p.d == 64 ? dispatch<64, true>(pass, p, s) : dispatch<128, true>(pass, p, s);
-  return p.d == 64 ? dispatch<64, false>(pass, p, s) : dispatch<128, false>(pass, p, s);
+  return p.dtype == FHOB_F16 ? dispatch_dims<true>(pass, p, s) : dispatch_dims<false>(pass, p, s);
 }
 
 }  // namespace fhob

@@ -25,7 +25,7 @@ class FhobProblem(C.Structure):
     _fields_ = [
         ("bh", C.c_int32), ("n_q", C.c_int32), ("n_k", C.c_int32), ("d", C.c_int32),
         ("dtype", C.c_int32), ("causal", C.c_int32), ("impl", C.c_int32), ("scale", C.c_float),
-        ("window", C.c_int32), ("reserved", C.c_int32),
+        ("window", C.c_int32), ("d_v", C.c_int32),
         ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p), ("d_o", C.c_void_p),
         ("ddq", C.c_void_p), ("ddk", C.c_void_p), ("ddv", C.c_void_p), ("lse", C.c_void_p),
         ("dq2", C.c_void_p), ("dk2", C.c_void_p), ("dv2", C.c_void_p), ("ddo", C.c_void_p),

@@ -33,8 +33,8 @@ def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sli
     """
     # the problem struct wants three cotangent tensors of the right shapes; they are not read
     prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, impl, need_outputs=False, window=sliding_window)
-    q, k = prob.keep[0], prob.keep[1]
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(k)
+    q, k, v = prob.keep[0], prob.keep[1], prob.keep[2]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     with torch.cuda.device(prob.device):
         _lib.check(_lib.load().fhob_backward(C.byref(prob.p), C.c_void_p(dq.data_ptr()), C.c_void_p(dk.data_ptr()),
                                              C.c_void_p(dv.data_ptr()), C.c_void_p(prob.stream)), "fhob_backward")

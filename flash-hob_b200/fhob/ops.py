@@ -76,15 +76,17 @@ class _Problem:
                 raise ValueError(f"{n} is on {t.device}, Q is on {dev}")
             if t.dtype != dt:
                 raise TypeError(f"{n} has dtype {t.dtype}, Q has {dt}")
-        self.out_shape_q, self.out_shape_k = Q.shape, K.shape
+        self.out_shapes = (Q.shape, K.shape, V.shape, dO.shape)   # dQ2, dK2, dV2, ddO
         t3 = [_fold(t, n) for n, t in zip(names, tensors)]
         q, k, v, o, do, ddq, ddk, ddv = t3
         bh, n_q, d = q.shape
-        n_k = k.shape[1]
+        n_k, d_v = k.shape[1], v.shape[2]
+        # two head dims (jax_refs/flash_impl.py:381-389): Q, K and their cotangents share one, V, O, dO, ddV the other
+        want_shapes = dict(Q=(bh, n_q, d), ddQ=(bh, n_q, d), K=(bh, n_k, d), ddK=(bh, n_k, d),
+                           V=(bh, n_k, d_v), ddV=(bh, n_k, d_v), O=(bh, n_q, d_v), dO=(bh, n_q, d_v))
         for n, t in zip(names, t3):
-            want = (bh, n_q, d) if n in ("Q", "O", "dO", "ddQ") else (bh, n_k, d)
-            if tuple(t.shape) != want:
-                raise ValueError(f"{n}: shape {tuple(t.shape)} does not match {want}")
+            if tuple(t.shape) != want_shapes[n]:
+                raise ValueError(f"{n}: shape {tuple(t.shape)} does not match {want_shapes[n]}")
         lse = L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)
         if tuple(lse.shape) != (bh, n_q) or L.device != dev:
             raise ValueError(f"L: expected {(bh, n_q)} on {dev}, got {tuple(L.shape)} on {L.device}")
@@ -104,6 +106,7 @@ class _Problem:
             self.ws = workspace
         p = _lib.FhobProblem()
         p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
+        p.d_v = 0 if d_v == d else d_v
         p.dtype = _lib.DTYPES[str(dt)]
         p.causal = 1 if is_causal else 0
         p.window = _window(is_causal, window)
@@ -114,7 +117,7 @@ class _Problem:
             p.o = None
         p.ddq, p.ddk, p.ddv, p.lse = (t.data_ptr() for t in (ddq, ddk, ddv, lse))
         if need_outputs and out is not None:
-            want = (q.shape, k.shape, k.shape, q.shape)
+            want = (q.shape, k.shape, v.shape, do.shape)
             if len(out) != 4:
                 raise ValueError("out: expected (dQ2, dK2, dV2, ddO)")
             folded = []
@@ -125,16 +128,15 @@ class _Problem:
             self.dq2, self.dk2, self.dv2, self.ddo = folded
             p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
         elif need_outputs:
-            self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(q)
-            self.dk2, self.dv2 = torch.empty_like(k), torch.empty_like(k)
+            self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(do)
+            self.dk2, self.dv2 = torch.empty_like(k), torch.empty_like(v)
             p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
         p.workspace, p.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
         self.p = p
         self.bh, self.n_q = bh, n_q
 
     def outputs(self):
-        return (self.dq2.reshape(self.out_shape_q), self.dk2.reshape(self.out_shape_k),
-                self.dv2.reshape(self.out_shape_k), self.ddo.reshape(self.out_shape_q))
+        return tuple(t.reshape(s) for t, s in zip((self.dq2, self.dk2, self.dv2, self.ddo), self.out_shapes))
 
     def status(self) -> int:
         """Synchronises the stream and returns the device status word."""
@@ -161,7 +163,11 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     Same positional signature and return order as the reference
     (fhog/triton_bwdbwd.py:558, :648).  Tensors are ``(BH, N, D)`` like the
     reference or ``(B, H, N, D)``; bfloat16 or float16 (tensor-core kernels,
-    fp32 accumulation) or float32 (CUDA-core kernels).  ``L`` is the logsumexp of
+    fp32 accumulation) or float32 (CUDA-core kernels).  ``V``, ``O``, ``dO``
+    and ``ddV`` may have a head dim of their own (the reference operator has a
+    single D, :577; its maths does not need that, jax_refs/flash_impl.py:381-389):
+    ``dV2`` and ``ddO`` then have it too; the tensor-core kernels take head dims
+    64 and 128 in any combination.  ``L`` is the logsumexp of
     the masked scaled scores, any float dtype (used as fp32).  ``O`` may be
     ``None`` for 16-bit inputs on the tensor-core path: ``D = rowsum(dO * O)``
     (reference :580) is then replaced by the mathematically equal
@@ -216,13 +222,13 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     allocator, so after the first call of a shape nothing is allocated on the device, and the
     results' pinned buffers come from torch's caching host allocator."""
     names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
-    shape_q, shape_k = mats[0].shape, mats[1].shape
+    out_shapes = (mats[0].shape, mats[1].shape, mats[2].shape, mats[4].shape)   # dQ2, dK2, dV2, ddO
     mats3 = [_fold(t, n) for t, n in zip(mats, names)]
     bh = mats3[0].shape[0]
     lse = (L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)).to(torch.float32)
     if lse.shape[0] != bh:
         raise ValueError(f"L: expected {bh} rows, got {tuple(L.shape)}")
-    want = (mats3[0], mats3[1], mats3[1], mats3[0])
+    want = (mats3[0], mats3[1], mats3[2], mats3[4])
     if out is None:
         outs_host = [torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True) for t in want]
     else:
@@ -267,8 +273,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
         main.synchronize()
         for status in status_host.tolist():
             _lib.check(status, "fhob_bwdbwd (device status)")
-    return (outs_host[0].reshape(shape_q), outs_host[1].reshape(shape_k), outs_host[2].reshape(shape_k),
-            outs_host[3].reshape(shape_q))
+    return tuple(t.reshape(s) for t, s in zip(outs_host, out_shapes))
 
 
 def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None,
@@ -290,12 +295,16 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     if q.device.type != "cuda" or str(q.dtype) not in _lib.DTYPES:
         raise ValueError("attention_forward needs CUDA bfloat16/float16/float32 tensors")
     bh, n_q, d = q.shape
+    d_v = v.shape[2]
+    if k.shape != (bh, k.shape[1], d) or v.shape[:2] != k.shape[:2]:
+        raise ValueError(f"K {tuple(k.shape)} / V {tuple(v.shape)} do not match Q {tuple(q.shape)}")
     if scale is None:
         scale = d ** -0.5
-    o = torch.empty_like(q) if need_o else None
+    o = torch.empty(bh, n_q, d_v, dtype=q.dtype, device=q.device) if need_o else None
     lse = torch.empty(bh, n_q, dtype=torch.float32, device=q.device)
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
+    p.d_v = 0 if d_v == d else d_v
     p.dtype = _lib.DTYPES[str(q.dtype)]
     if impl not in _lib.IMPL:
         raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
@@ -311,7 +320,7 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
                                     C.c_void_p(lse.data_ptr()), C.c_void_p(stream)), "fhob_forward")
         if check:
             _lib.check(lib.fhob_read_status(C.byref(p), C.c_void_p(stream)), "fhob_forward (device status)")
-    return (o.reshape(shape_q) if need_o else None), lse.reshape(shape_q[:-1])
+    return (o.reshape(*shape_q[:-1], d_v) if need_o else None), lse.reshape(shape_q[:-1])
 
 
 def produce_L(Q, K, is_causal: bool = False, scale=None, sliding_window: Optional[int] = None):

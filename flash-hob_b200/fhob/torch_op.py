@@ -29,5 +29,5 @@ def bwdbwd(Q: torch.Tensor, K: torch.Tensor, V: torch.Tensor, O: torch.Tensor, d
 def _(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal=False, sliding_window=0):
     return (torch.empty_like(Q, memory_format=torch.contiguous_format),
             torch.empty_like(K, memory_format=torch.contiguous_format),
-            torch.empty_like(K, memory_format=torch.contiguous_format),
-            torch.empty_like(Q, memory_format=torch.contiguous_format))
+            torch.empty_like(V, memory_format=torch.contiguous_format),
+            torch.empty_like(dO, memory_format=torch.contiguous_format))

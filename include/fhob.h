@@ -61,7 +61,8 @@ typedef struct FhobProblem {
   int32_t bh;      /* folded batch*heads */
   int32_t n_q;     /* query rows per head */
   int32_t n_k;     /* key rows per head */
-  int32_t d;       /* head dim, shared by q/k and v like the reference (:577) */
+  int32_t d;       /* head dim of q, k, ddq, ddk, dq2, dk2 (and of the v side too when d_v is 0, like the
+                      reference, which has a single D: :577) */
   int32_t dtype;   /* FHOB_BF16, FHOB_F16 or FHOB_F32 */
   int32_t causal;  /* 0, or 1 = bottom-right aligned causal mask: key j visible to query i iff i + n_k - n_q >= j.
                       With n_k < n_q the first n_q - n_k queries see no key at all: their dQ2 and ddO rows are
@@ -71,23 +72,24 @@ typedef struct FhobProblem {
   float scale;     /* softmax scale */
   int32_t window;  /* sliding_window_length of jax_refs/flash_impl.py:86-91: 0 = none; W > 0 (needs causal = 1)
                       additionally hides keys with (i + n_k - n_q) - j >= W */
-  int32_t reserved; /* must be 0 */
+  int32_t d_v;     /* head dim of v, ddv, o, d_o, ddo, dv2 when it differs from d (the reference's maths allows
+                      two head dims, jax_refs/flash_impl.py:381-389); 0 = same as d */
   /* inputs, device pointers */
   const void* q;   /* (bh, n_q, d) */
   const void* k;   /* (bh, n_k, d) */
-  const void* v;   /* (bh, n_k, d) */
-  const void* o;   /* (bh, n_q, d) forward output; may be NULL for fhob_bwdbwd / fhob_pass12 on the tensor-core
+  const void* v;   /* (bh, n_k, d_v) */
+  const void* o;   /* (bh, n_q, d_v) forward output; may be NULL for fhob_bwdbwd / fhob_pass12 on the tensor-core
                       path: D = rowsum(dO * O) (reference :580) is then replaced by the equal sum_j P dP */
-  const void* d_o; /* (bh, n_q, d) cotangent of o in the first backward */
+  const void* d_o; /* (bh, n_q, d_v) cotangent of o in the first backward */
   const void* ddq; /* (bh, n_q, d) cotangent of dQ */
   const void* ddk; /* (bh, n_k, d) cotangent of dK */
-  const void* ddv; /* (bh, n_k, d) cotangent of dV */
+  const void* ddv; /* (bh, n_k, d_v) cotangent of dV */
   const float* lse; /* (bh, n_q) fp32 logsumexp of the masked scaled scores */
   /* outputs, device pointers, same element type as the inputs */
   void* dq2; /* (bh, n_q, d) */
   void* dk2; /* (bh, n_k, d) */
-  void* dv2; /* (bh, n_k, d) */
-  void* ddo; /* (bh, n_q, d) */
+  void* dv2; /* (bh, n_k, d_v) */
+  void* ddo; /* (bh, n_q, d_v) */
   /* scratch: fhob_workspace_bytes(bh, n_q) bytes, 256-byte aligned */
   void* workspace;
   size_t workspace_bytes;
@@ -197,8 +199,8 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
  * window, impl; writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).
  * `o_out` may be NULL when only the logsumexp is wanted (the role of
  * produce_L): the P V product is then skipped altogether.
- * 16-bit inputs with d in {64, 128} run on the tensor cores (impl AUTO or
- * TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
+ * 16-bit inputs with d = d_v in {64, 128} run on the tensor cores (impl AUTO
+ * or TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
  * that ran out) go to the status word at the start of p->workspace, or, when
  * p->workspace is NULL, to a word the library keeps per device; either is
  * cleared by the call and read with fhob_read_status(p, stream).

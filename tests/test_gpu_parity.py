@@ -334,7 +334,7 @@ def test_autograd_grad_of_grad(causal):
     x = make_inputs(2, 128, 256, 64, seed=93, dtype=torch.float64)
     ref = O.bwdbwd_autograd(*x.values(), 0.125, causal)
     ref_first = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], 0.125, causal)
-    for dtype, tol in ((torch.float32, 2e-4), (torch.bfloat16, 3e-2)):
+    for dtype, tol in ((torch.float32, TOL_F32), (torch.bfloat16, TOL_BF16)):
         q, k, v, do = (x[n].to(dtype).cuda().requires_grad_(True) for n in ("q", "k", "v", "do"))
         out = fhob.attention(q, k, v, 0.125, is_causal=causal)
         dq, dk, dv = torch.autograd.grad(out, (q, k, v), do, create_graph=True)
@@ -415,7 +415,7 @@ def test_sliding_window_forward_backward_and_autograd():
     cot = tuple(x[n].float().cuda() for n in ("ddq", "ddk", "ddv"))
     got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
     for n, g, r in zip(OUT_NAMES, got, ref):
-        assert O.rel_err(g, r) < 2e-4, n
+        assert O.rel_err(g, r) < TOL_F32, n
 
 
 def test_sliding_window_argument_errors():
@@ -718,6 +718,81 @@ def test_causal_queries_without_any_visible_key(bh, nq, nk, d, window, dtype, im
                                  lse.float().cuda(), scale, check=True, **kw)
         for n, g, r in zip(OUT_NAMES, got2, ref):
             assert torch.isfinite(g).all() and O.rel_err(g, r) < tol, n
+
+
+def _two_dim_inputs(bh, nq, nk, dqk, dv, seed):
+    g = torch.Generator().manual_seed(seed)
+    shapes = dict(q=(bh, nq, dqk), k=(bh, nk, dqk), v=(bh, nk, dv), do=(bh, nq, dv),
+                  ddq=(bh, nq, dqk), ddk=(bh, nk, dqk), ddv=(bh, nk, dv))
+    return {n: torch.randn(s, generator=g).bfloat16().double() for n, s in shapes.items()}
+
+
+@pytest.mark.parametrize("dtype,impl,tol", [(torch.bfloat16, "tcgen05", TOL_BF16), (torch.bfloat16, "simt", TOL_BF16),
+                                            (torch.float32, "auto", TOL_F32)])
+@pytest.mark.parametrize("causal,window", [(False, None), (True, None), (True, 90)])
+@pytest.mark.parametrize("bh,nq,nk,dqk,dv", [(2, 256, 384, 64, 128), (2, 384, 384, 128, 64), (1, 200, 328, 64, 128),
+                                             (3, 130, 259, 128, 64)])
+def test_value_head_dim_differs_from_query_key_head_dim(bh, nq, nk, dqk, dv, causal, window, dtype, impl, tol):
+    """d_v != d_qk: V, O, dO, ddV (and the results dV2, ddO) have a head dim of their own, as in the
+    reference's maths (jax_refs/flash_impl.py:381-389 uses d_in = 256, d_out = 512; its Triton
+    operator cannot, fhog/triton_bwdbwd.py:577).  Operator, row statistics, forward and first
+    backward against the oracle, which takes any two dims."""
+    import fhob
+    import math
+    wl = math.inf if window is None else window
+    x = _two_dim_inputs(bh, nq, nk, dqk, dv, seed=411)
+    scale = dqk ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal, sliding_window_length=wl)
+    assert ref[2].shape == (bh, nk, dv) and ref[3].shape == (bh, nq, dv)
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=wl)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=wl)
+    dev = {k: v.to(dtype).cuda() for k, v in x.items()}
+    kw = dict(is_causal=causal, sliding_window=window, impl=impl)
+    args = (dev["q"], dev["k"], dev["v"], o_ref.to(dtype).cuda(), dev["do"], dev["ddq"], dev["ddk"], dev["ddv"],
+            l_ref.float().cuda(), scale)
+    got = fhob.flash_bwdbwd(*args, check=True, **kw)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert g.shape == r.shape and O.rel_err(g, r) < tol, n
+    if window is None:
+        sd, sdd, sb = O.bwdbwd_row_stats(*x.values(), scale, causal)
+        for fused in ((False, True) if impl != "auto" else (False,)):
+            res = fhob.run_passes(*args, is_causal=causal, impl=impl, upto=2, fused12=fused)
+            assert res["status"] == 0
+            assert O.rel_err(res["d"], sd) < max(tol, 5e-3 if dtype != torch.float32 else 0)
+            assert O.rel_err(res["dd"], sdd) < tol and O.rel_err(res["b"], sb) < tol
+    if dtype != torch.float32 and impl == "tcgen05":
+        got = fhob.flash_bwdbwd(*args[:3], None, *args[4:], check=True, **kw)     # D from the sweep
+        for n, g, r in zip(OUT_NAMES, got, ref):
+            assert O.rel_err(g, r) < tol, n
+    # the producers either side (CUDA cores when the two dims differ)
+    fkw = dict(kw, impl="auto")
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **fkw)
+    assert o.shape == (bh, nq, dv) and O.rel_err(o, o_ref) < tol and O.rel_err(lse, l_ref) < 1e-5
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **fkw)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, causal, sliding_window_length=wl)
+    for n, g, r in zip(("dq", "dk", "dv"), first, first_ref):
+        assert g.shape == r.shape and O.rel_err(g, r) < tol, n
+
+
+def test_two_head_dims_through_autograd_and_host_buffers():
+    """fhob.attention differentiated twice with d_v != d_qk, and the host-buffer path of the operator."""
+    import fhob
+    x = _two_dim_inputs(2, 192, 320, 128, 64, seed=413)
+    scale = 128 ** -0.5
+    ref = O.bwdbwd_autograd(*x.values(), scale, True)
+    q, k, v, do = (x[n].bfloat16().cuda().requires_grad_(True) for n in ("q", "k", "v", "do"))
+    out = fhob.attention(q, k, v, scale, is_causal=True)
+    dq, dk, dv = torch.autograd.grad(out, (q, k, v), do, create_graph=True)
+    cot = tuple(x[n].bfloat16().cuda() for n in ("ddq", "ddk", "ddv"))
+    got = torch.autograd.grad((dq, dk, dv), (q, k, v, do), cot)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
+    o = O.attn_fwd(x["q"], x["k"], x["v"], scale, True).bfloat16()
+    lse = O.attn_lse(x["q"], x["k"], scale, True).float()
+    host = [x[n].bfloat16() for n in ("q", "k", "v")] + [o] + [x[n].bfloat16() for n in ("do", "ddq", "ddk", "ddv")]
+    got = fhob.flash_bwdbwd(*host, lse, scale, is_causal=True)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert g.device.type == "cpu" and g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
 
 
 def test_preallocated_outputs_and_workspace():
