@@ -62,8 +62,9 @@ EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # traffic of a launch grows in proportion to its heads).
 DRAM_BYTES_PER_HEAD = {("cfg5", "pass12"): 191.01e6 / 16, ("cfg5", "pass3"): 207.72e6 / 16,
                        ("cfg5", "pass4"): 229.56e6 / 16}
-KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, 64, 1, 0>",
-                "pass3": "tc_pass_kernel<3, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, 64, 0, 0>"}
+# template arguments: pass, head dim of q/k, head dim of v, streamed rows, fused dd+b sweep, fp16 storage
+KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, {d}, 64, 1, 0>",
+                "pass3": "tc_pass_kernel<3, {d}, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, {d}, 64, 0, 0>"}
 METRIC = "double_backward_attention_tflops"
 
 _JSON_FD = None
@@ -376,7 +377,25 @@ def competitor_child(args):
     case = Case(w, heads, dev, seed=777)
     t0 = time.time()
     from fhog.triton_bwdbwd import bwdbwd_kernel_stage1, bwdbwd_kernel_stage2, flash_bwdbwd as ref_bwdbwd
-    theirs = ref_bwdbwd(*case.args)          # first call: torch.compile + Triton autotune over its config list
+    how = "as shipped: fhog.flash_bwdbwd, a torch.compile(fullgraph=True) wrapper around two autotuned Triton kernels"
+    as_shipped_error = None
+    try:
+        theirs = ref_bwdbwd(*case.args)      # first call: torch.compile + Triton autotune over its config list
+    except Exception as e:  # noqa: BLE001
+        # The compiled wrapper can fail with this image's torch/triton pair.  The function under
+        # the wrapper is the same unmodified reference code; calling it directly only skips
+        # torch.compile (the Triton kernels and their autotuning are untouched).
+        eager = getattr(ref_bwdbwd, "_torchdynamo_orig_callable", None) or getattr(ref_bwdbwd, "__wrapped__", None)
+        lines = [l for l in str(e).strip().splitlines() if l.strip()]
+        as_shipped_error = f"{type(e).__name__}: " + " | ".join(lines[-3:])[:500]
+        if eager is None:
+            print(json.dumps(dict(error=as_shipped_error)))
+            return
+        import importlib
+        importlib.import_module("torch._dynamo").reset()
+        ref_bwdbwd = eager
+        how = "the function under the reference's torch.compile wrapper, called directly (the wrapper itself failed)"
+        theirs = ref_bwdbwd(*case.args)
     torch.cuda.synchronize()
     setup_s = time.time() - t0
     for _ in range(2):
@@ -404,7 +423,8 @@ def competitor_child(args):
     oracle_err_theirs = case.check_head(theirs, heads - 1)
     oracle_err_ours = case.check_head(ours, heads - 1)
     print(json.dumps(dict(
-        workload=args.workload, heads=heads, steps=args.steps, setup_s=round(setup_s, 1),
+        workload=args.workload, heads=heads, steps=args.steps, setup_s=round(setup_s, 1), how=how,
+        as_shipped_error=as_shipped_error,
         reference_triton=dict(ms_per_step=round(ms_ref, 4), tflops_alg=round(f_alg(w, heads) / ms_ref / 1e9, 1),
                               autotuned_stage1=cfg(bwdbwd_kernel_stage1), autotuned_stage2=cfg(bwdbwd_kernel_stage2),
                               max_rel_err_vs_fp64_oracle=oracle_err_theirs),
@@ -447,6 +467,7 @@ def main():
                     "smaller values give the small cases profiler captures need")
     ap.add_argument("--min-timed-s", type=float, default=1.0,
                     help="rounds of --steps steps are repeated until at least this much device time is covered")
+    ap.add_argument("--min-rounds", type=int, default=3, help="at least this many rounds (the median round is reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-producers", action="store_true", help="do not time the forward / first-backward kernels")
@@ -516,7 +537,7 @@ def main():
     warmup = done_w
     est_ms = (time.time() - t_w) * 1e3 / done_w
     # rounds of exactly `steps` steps; enough of them to cover --min-timed-s of device time
-    rounds = max(1, min(50, math.ceil(args.min_timed_s * 1e3 / max(est_ms * args.steps, 1e-3))))
+    rounds = max(1, args.min_rounds, min(50, math.ceil(args.min_timed_s * 1e3 / max(est_ms * args.steps, 1e-3))))
     if world > 1:
         t = torch.tensor([rounds], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -113,7 +113,30 @@ EncodeTiledFn encode_fn() {
 }
 
 // (bh, n, d) 16-bit row-major tensor, box = 64 columns x `rows` rows of one head, 128-byte swizzle.
+// Encoded maps are kept in a small per-thread table: a training step calls the operator with the
+// same tensors again and again, and an encode costs a few microseconds of host time per map.
+struct MapKey {
+  const void* base;
+  int bh, n, d, rows, f16;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && bh == o.bh && n == o.n && d == o.d && rows == o.rows && f16 == o.f16;
+  }
+};
+
 int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, bool f16) {
+  constexpr int kSlots = 64;
+  struct Entry {
+    MapKey key;
+    CUtensorMap map;
+  };
+  static thread_local Entry table[kSlots];
+  static thread_local int used = 0, next = 0;
+  const MapKey key{base, bh, n, d, rows, f16 ? 1 : 0};
+  for (int i = 0; i < used; ++i)
+    if (table[i].key == key) {
+      *m = table[i].map;
+      return FHOB_OK;
+    }
   EncodeTiledFn fn = encode_fn();
   if (!fn) {
     set_cuda_error_text("cuTensorMapEncodeTiled entry point not available");
@@ -132,6 +155,40 @@ int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, b
     set_cuda_error_text(buf);
     return FHOB_ERR_CUDA;
   }
+  Entry& e = table[next];
+  e.key = key;
+  e.map = *m;
+  next = (next + 1) % kSlots;
+  if (used < kSlots) ++used;
+  return FHOB_OK;
+}
+
+// Raises the dynamic shared-memory limit of `kernel` once per device and host thread (it is a
+// per-function, per-device attribute; setting it again on every launch costs a driver call).
+template <class K>
+int allow_smem(K kernel, int bytes) {
+  constexpr int kSlots = 96;
+  struct Entry {
+    const void* fn;
+    unsigned long long devices;
+  };
+  static thread_local Entry table[kSlots];
+  static thread_local int used = 0;
+  int dev = 0;
+  FHOB_CUDA_OK(cudaGetDevice(&dev));
+  const unsigned long long bit = (dev >= 0 && dev < 64) ? (1ull << dev) : 0;
+  const void* fn = reinterpret_cast<const void*>(kernel);
+  Entry* e = nullptr;
+  for (int i = 0; i < used && !e; ++i)
+    if (table[i].fn == fn) e = &table[i];
+  if (e && bit && (e->devices & bit)) return FHOB_OK;
+  FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (!e && used < kSlots) {
+    e = &table[used++];
+    e->fn = fn;
+    e->devices = 0;
+  }
+  if (e) e->devices |= bit;
   return FHOB_OK;
 }
 

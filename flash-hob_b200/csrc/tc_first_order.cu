@@ -593,7 +593,10 @@ int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
   const int n_stat = MODE == FO_BK ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
   constexpr auto kernel = fo_kernel<MODE, D, F16>;
-  FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  {
+    const int st_attr = allow_smem(kernel, C::SMEM_BYTES);
+    if (st_attr != FHOB_OK) return st_attr;
+  }
   const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
   if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
   kernel<<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);

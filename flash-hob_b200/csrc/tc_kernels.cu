@@ -785,7 +785,10 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = PASS == 4 ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
-  FHOB_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+  {
+    const int st_attr = allow_smem(kernel, C::SMEM_BYTES);
+    if (st_attr != FHOB_OK) return st_attr;
+  }
   const long long blocks = static_cast<long long>(tp.tiles_per_head) * p.bh;
   if (blocks > 0x7fffffffLL) return FHOB_ERR_SHAPE;
   kernel<<<static_cast<unsigned>(blocks), NTHREADS, C::SMEM_BYTES, s>>>(tp);
