@@ -123,7 +123,11 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->d > 128 || dv > 128) return FHOB_ERR_SHAPE;
   if (!p->workspace || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) return FHOB_ERR_WORKSPACE;
   if (p->workspace_bytes < fhob_workspace_bytes(p->bh, p->n_q)) return FHOB_ERR_WORKSPACE;
-  if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) return FHOB_ERR_SHAPE;
+  if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) {
+    // fp32 with both head dims 64 runs on the tensor cores if the workspace also holds the bf16 hi/lo copies
+    if (p->dtype == FHOB_F32 && p->d == 64 && dv == 64) return FHOB_ERR_WORKSPACE;
+    return FHOB_ERR_SHAPE;
+  }
   return FHOB_OK;
 }
 
@@ -156,7 +160,8 @@ const char* fhob_strerror(int status) {
     case FHOB_ERR_SHAPE: return "shape not supported (head dims must keep rows 16-byte aligned and be <= 128; "
                                 "the tensor-core kernels need 16-bit elements and head dims in {64,128})";
     case FHOB_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
-    case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes()";
+    case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes() "
+                                    "(fp32 on the tensor cores: smaller than fhob_workspace_bytes_problem())";
     case FHOB_ERR_CUDA: return "a CUDA call failed (see fhob_last_cuda_error)";
     case FHOB_ERR_ARCH: return "the tensor-core kernels need a compute capability 10.x device";
     case FHOB_ERR_STATIC_LIMIT: return "bh*n_q exceeds FHOB_STATIC_SCRATCH_MAX_ROWS, the capacity of the built-in "
@@ -171,6 +176,13 @@ const char* fhob_strerror(int status) {
 
 const char* fhob_last_cuda_error(void) { return g_cuda_error; }
 
+size_t fhob_workspace_bytes_problem(const FhobProblem* p) {
+  if (!p || p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0) return 0;
+  if (p->dtype == FHOB_F32 && p->impl != FHOB_IMPL_SIMT && p->d == 64 && head_dim_v(*p) == 64)
+    return split_workspace_bytes(*p);
+  return fhob_workspace_bytes(p->bh, p->n_q);
+}
+
 size_t fhob_workspace_bytes(int32_t bh, int32_t n_q) {
   if (bh <= 0 || n_q <= 0) return 0;
   size_t rows = static_cast<size_t>(bh) * static_cast<size_t>(row_stride(n_q));
@@ -178,8 +190,14 @@ size_t fhob_workspace_bytes(int32_t bh, int32_t n_q) {
   return kWorkspaceHeaderBytes + 4 * rows * sizeof(float) + kWorkspaceTailBytes;
 }
 
-static int run_prepass(const FhobProblem* p, void* stream) {
+// `for_operator`: the passes of the double backward follow (not the first backward), so an fp32
+// problem headed for the tensor cores also gets its bf16 hi/lo copies made here
+static int run_prepass(const FhobProblem* p, void* stream, bool for_operator = true) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (for_operator && p->dtype == FHOB_F32 && use_tc(*p)) {
+    int st = tc_split_inputs(*p, s);
+    if (st != FHOB_OK) return st;
+  }
   RowVectors rv = row_vectors(*p);
   long rows = static_cast<long>(p->bh) * p->n_q;
   const int warps = 8;
@@ -317,7 +335,7 @@ int fhob_backward(const FhobProblem* p, void* dq, void* dk, void* dv, void* stre
   int st = validate(p, false, false);
   if (st != FHOB_OK) return st;
   if (!aligned16(dq) || !aligned16(dk) || !aligned16(dv)) return FHOB_ERR_ALIGN;
-  st = run_prepass(p, stream);  // stores -L*log2(e) and -D in the workspace
+  st = run_prepass(p, stream, false);  // stores -L*log2(e) and -D in the workspace
   if (st != FHOB_OK) return st;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc = p->impl == FHOB_IMPL_TCGEN05 || (p->impl == FHOB_IMPL_AUTO && tc_first_order_supported(*p));

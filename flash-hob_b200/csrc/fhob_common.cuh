@@ -59,6 +59,28 @@ inline RowVectors row_vectors(const FhobProblem& p) {
   return r;
 }
 
+// fp32 problems on the tensor cores: bf16 hi/lo copies of the seven inputs, rows of [hi(64) | lo(64)],
+// stored behind the row vectors in the workspace (each copy has the bytes of its fp32 original).
+struct SplitBuffers {
+  void *q, *ddq, *d_o, *k, *ddk, *v, *ddv;
+};
+inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+inline size_t split_workspace_bytes(const FhobProblem& p) {
+  const size_t q_bytes = align256(static_cast<size_t>(p.bh) * p.n_q * 256);
+  const size_t k_bytes = align256(static_cast<size_t>(p.bh) * p.n_k * 256);
+  return align256(fhob_workspace_bytes(p.bh, p.n_q)) + 3 * q_bytes + 4 * k_bytes;
+}
+inline SplitBuffers split_buffers(const FhobProblem& p) {
+  const size_t q_bytes = align256(static_cast<size_t>(p.bh) * p.n_q * 256);
+  const size_t k_bytes = align256(static_cast<size_t>(p.bh) * p.n_k * 256);
+  char* b = static_cast<char*>(p.workspace) + align256(fhob_workspace_bytes(p.bh, p.n_q));
+  SplitBuffers s;
+  s.q = b; s.ddq = b + q_bytes; s.d_o = b + 2 * q_bytes;
+  b += 3 * q_bytes;
+  s.k = b; s.ddk = b + k_bytes; s.v = b + 2 * k_bytes; s.ddv = b + 3 * k_bytes;
+  return s;
+}
+
 // Mask of the reference (jax_refs/flash_impl.py:86-91): with off = n_k - n_q, key j is visible to
 // query i iff 0 <= i + off - j, and i + off - j < window when a sliding window is set.
 __host__ __device__ inline bool pair_visible(int qi, int kj, int off, int causal, int window) {
@@ -112,6 +134,8 @@ int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream
 
 // tcgen05 / TMEM / TMA kernels (bf16, d in {64,128}): tc_kernels.cu
 bool tc_supported(const FhobProblem& p);
+bool tc_split_supported(const FhobProblem& p);            // fp32 on the tensor cores (split operands)
+int tc_split_inputs(const FhobProblem& p, cudaStream_t s);  // writes the hi/lo copies into the workspace
 int tc_pass(int pass, const FhobProblem& p, cudaStream_t s);
 
 // tensor-core forward (O, L) and first backward (dQ, dK, dV): tc_first_order.cu

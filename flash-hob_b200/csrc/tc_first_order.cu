@@ -669,7 +669,9 @@ int tc_selftest_expired_wait(int* status, cudaStream_t s) {
 }
 
 // the first-order kernels take one head dim; problems with d_v != d run on the CUDA-core kernels
-bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p) && head_dim_v(p) == p.d; }
+bool tc_first_order_supported(const FhobProblem& p) {
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && tc_supported(p) && head_dim_v(p) == p.d;
+}
 
 int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;

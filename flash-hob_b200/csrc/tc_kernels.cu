@@ -192,6 +192,35 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
   }
 }
 
+// fp32 problems on the tensor cores (SPLIT): every fp32 operand x travels as two bf16 numbers,
+// hi = bf16(x) and lo = bf16(x - hi), and a contraction becomes three kind::f16 products with fp32
+// accumulation, hi.hi + hi.lo + lo.hi (the lo.lo term, 2^-16 of the result, is dropped).  A row of
+// a split tensor in memory is [hi(64) | lo(64)], which is exactly the two 64-column boxes of a
+// 128-wide tile, so tile shapes, shared-memory layout and the TMEM budget are those of head dim
+// 128; the head dim itself is 64.  The 16-bit tiles the elementwise warps hand back (P, ddP, dS,
+// dS2) are split the same way: a thread's 32 fp32 columns of an accumulator take 16 packed columns
+// of hi values followed by 16 of lo values.
+__device__ __forceinline__ void split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x, y);
+  lo = pack_bf16(x - __uint_as_float(hi << 16), y - __uint_as_float(hi & 0xffff0000u));
+}
+
+// D (+)= A . B^T for split operands: boxes (hi, hi), (hi, lo), (lo, hi), four K = 16 steps each.
+template <int A_BOX, int B_BOX>
+__device__ __forceinline__ void gemm_ss_split(bool leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                              uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int term = 0; term < 3; ++term) {
+    const int ab = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      const uint32_t a = a_lo + ((ab * A_BOX + ks * 32) >> 4);
+      const uint32_t b = b_lo + ((bb * B_BOX + ks * 32) >> 4);
+      umma_ss_split(d_tmem, a, b, kDescHi, idesc, (accumulate || term > 0 || ks > 0) ? 1u : 0u, leader);
+    }
+  }
+}
+
 // Passes 3 and 4 work on a thread's 32 columns of a 64-row streamed tile at once, two columns
 // per packed fp32 instruction (fma/mul/add .f32x2).
 // First half of a tile: S, A2 -> P = exp2(S*sl2 + nlc), t = scale*A2 - dd; writes ddP = P t (and P
@@ -202,7 +231,7 @@ __device__ __forceinline__ void ew_reduce(uint32_t acc, int col_base, const EwCt
 // (measured: pass 3 3-4 % faster; pass 4, which is at the register limit, up to 8 % slower).
 __host__ __device__ constexpr bool early_s(int pass) { return FHOB_EARLY_S && pass == 3; }
 
-template <int PASS, bool MASKED, bool F16, class B>
+template <int PASS, bool MASKED, bool F16, bool SPLIT, class B>
 __device__ __forceinline__ bool ew_half_a(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           float2 (&ps)[16], float2 (&tt)[16], uint64_t* a2_full, uint32_t parity,
                                           B* bars, int* status) {
@@ -213,7 +242,7 @@ __device__ __forceinline__ bool ew_half_a(uint32_t acc, int col_base, int col_in
   tmem_ld32(acc + 0 * BN, s);
   if (!kEarlyS) tmem_ld32(acc + 1 * BN, a2);
   tmem_wait_ld();
-  uint32_t w_ddp[16], w_p[16];
+  uint32_t w_ddp[16], w_p[16], w_ddp_lo[16], w_p_lo[16];
   const float2 sl2 = make_float2(c.sl2, c.sl2), scale = make_float2(c.scale, c.scale);
   auto exps = [&](int j4) {
     float c_nlc[4];
@@ -267,19 +296,28 @@ __device__ __forceinline__ bool ew_half_a(uint32_t acc, int col_base, int col_in
       const float2 pr = ps[j / 2];
       const float2 ddp = __fmul2_rn(pr, t);
       tt[j / 2] = t;
-      w_ddp[j / 2] = pack16<F16>(ddp.x, ddp.y);
-      if (PASS == 3) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
+      if constexpr (SPLIT) {
+        split_pack(ddp.x, ddp.y, w_ddp[j / 2], w_ddp_lo[j / 2]);
+        if (PASS == 3) split_pack(pr.x, pr.y, w_p[j / 2], w_p_lo[j / 2]);
+      } else {
+        w_ddp[j / 2] = pack16<F16>(ddp.x, ddp.y);
+        if (PASS == 3) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
+      }
     }
   }
   // the 16-bit tiles overwrite accumulator columns this thread has already consumed
   tmem_st16(acc + 1 * BN, w_ddp);
   if (PASS == 3) tmem_st16(acc + 0 * BN, w_p);
+  if constexpr (SPLIT) {
+    tmem_st16(acc + 1 * BN + 16, w_ddp_lo);
+    if (PASS == 3) tmem_st16(acc + 0 * BN + 16, w_p_lo);
+  }
   return true;
 }
 
 // Second half: dP' = dP - D, X' = X - D*dd - b; writes P dP' and P (dP' t + X'), i.e. dS/scale and
 // dS2/scale: the factor `scale` is applied once to the finished dQ2 / dK2 accumulator instead.
-template <int PASS, bool MASKED, bool F16>
+template <int PASS, bool MASKED, bool F16, bool SPLIT>
 __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in_tile, const EwCtx& c,
                                           const float2 (&ps)[16], const float2 (&tt)[16]) {
   constexpr bool kQStat = PASS != 4;
@@ -288,7 +326,7 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
   tmem_ld32(acc + 2 * BN, dp);
   tmem_ld32(acc + 3 * BN, x);
   tmem_wait_ld();
-  uint32_t w_ds[16], w_ds2[16];
+  uint32_t w_ds[16], w_ds2[16], w_ds_lo[16], w_ds2_lo[16];
 #pragma unroll
   for (int j4 = 0; j4 < 8; ++j4) {
     float c_k1[4], c_k23[4];
@@ -313,17 +351,27 @@ __device__ __forceinline__ void ew_half_b(uint32_t acc, int col_base, int col_in
         ds.x = ok0 ? ds.x : 0.f;   ds.y = ok1 ? ds.y : 0.f;
         ds2.x = ok0 ? ds2.x : 0.f; ds2.y = ok1 ? ds2.y : 0.f;
       }
-      w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
-      w_ds2[j / 2] = pack16<F16>(ds2.x, ds2.y);
+      if constexpr (SPLIT) {
+        split_pack(ds.x, ds.y, w_ds[j / 2], w_ds_lo[j / 2]);
+        split_pack(ds2.x, ds2.y, w_ds2[j / 2], w_ds2_lo[j / 2]);
+      } else {
+        w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
+        w_ds2[j / 2] = pack16<F16>(ds2.x, ds2.y);
+      }
     }
   }
   tmem_st16(acc + 2 * BN, w_ds);
   tmem_st16(acc + 3 * BN, w_ds2);
+  if constexpr (SPLIT) {
+    tmem_st16(acc + 2 * BN + 16, w_ds_lo);
+    tmem_st16(acc + 3 * BN + 16, w_ds2_lo);
+  }
 }
 
-template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false>
+template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_constant__ TcParams p) {
   static_assert(FUSED == 0 || PASS == 2, "only pass 2 has a fused form");
+  static_assert(!SPLIT || (DQK == 128 && DV == 128 && !F16), "split fp32 operands are [hi(64) | lo(64)] bf16 rows");
   using C = Cfg<PASS, DQK, DV, BN>;
   constexpr bool kQStat = PASS != 4;
   // passes 1, 2: a third warp issues the second product of group A (their tensor pipe has the room;
@@ -452,6 +500,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       constexpr uint32_t idesc_s2 = umma_idesc_bf16(BM, 2 * BN, false, false, F16);  // a stacked pair
       constexpr uint32_t idesc_o0 = umma_idesc_bf16(BM, DQK, false, true, F16);  // dQ2 | dK2
       constexpr uint32_t idesc_o1 = umma_idesc_bf16(BM, DV, false, true, F16);   // ddO | dV2
+      constexpr uint32_t idesc_o64 = umma_idesc_bf16(BM, 64, false, true, F16);  // split operands: the hi box alone
       constexpr int kStatBox = BM * 128;
       // low descriptor words of the tiles: K-major use (LBO field unused, set to 1) and MN-major
       // use of streamed tile i (LBO = distance between its two 64-column boxes)
@@ -464,6 +513,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         return slot_lo - (1u << 16) + (C::strm_base(i) >> 4) + (static_cast<uint32_t>(C::strm_box(i) >> 4) << 16);
       };
       bool ok = wait_all(&bars->stat_full, 0);
+      // one score-shaped product: contraction over KD columns, or over hi/lo boxes for split operands
+      auto scores = [&](auto kd, auto b_box, uint32_t d, uint32_t a, uint32_t b, uint32_t idesc, bool accumulate) {
+        if constexpr (SPLIT) gemm_ss_split<kStatBox, decltype(b_box)::value>(leader, d, a, b, idesc, accumulate);
+        else gemm_ss<decltype(kd)::value, kStatBox, decltype(b_box)::value>(leader, d, a, b, idesc, accumulate);
+      };
+      using KQ = std::integral_constant<int, DQK>;
+      using KV = std::integral_constant<int, DV>;
+      using Box0 = std::integral_constant<int, C::strm_box(0)>;
+      using Box2 = std::integral_constant<int, C::strm_box(2)>;
 
       // score-shaped products of this chain for tile `it` (waits for the tile's shared-memory slot)
       //   chain 0, group A: [S | stat0.strm1^T] as one N = 2*BN product, then A2 += stat1.strm0^T
@@ -474,20 +532,20 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         tc_fence_after();
         const uint32_t sl = strm_lo + slot * kSlot16;
         if (chain == 0) {
-          gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
+          scores(KQ{}, Box0{}, acc, stat_lo, k_lo(sl, 0), idesc_s2, false);
           if (kThirdIssuer) {
             // A2 += stat1 . strm0^T is issued by the third warp, strictly behind the stacked product
             // so that the order of the fp32 accumulation (and with it every result bit) is fixed
             if (leader) mbar_arrive(&bars->a2_go);
           } else {
             if (early_s(PASS)) commit(&bars->s_ready);
-            gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_i(1), k_lo(sl, 0), idesc_s1, true);
+            scores(KQ{}, Box0{}, acc + BN, stat_i(1), k_lo(sl, 0), idesc_s1, true);
           }
         } else if (PASS == 4) {
-          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s1, false);
-          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 3 * BN, stat_i(3), k_lo(sl, 2), idesc_s1, false);
+          scores(KV{}, Box2{}, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s1, false);
+          scores(KV{}, Box2{}, acc + 3 * BN, stat_i(3), k_lo(sl, 2), idesc_s1, false);
         } else {
-          gemm_ss<DV, kStatBox, C::strm_box(2)>(leader, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s2, false);
+          scores(KV{}, Box2{}, acc + 2 * BN, stat_i(2), k_lo(sl, 2), idesc_s2, false);
         }
         return true;
       };
@@ -516,12 +574,19 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           ok = wait_all(&bars->p_full[chain], it & 1);
           if (!ok) break;
           tc_fence_after();
+          // one output product, A = 16-bit tile in TMEM; split operands: A_hi . [B_hi | B_lo] fills
+          // both 64-column halves of the accumulator (they are added in the epilogue), then
+          // A_lo . B_hi goes on top of the first half
+          auto outputs = [&](uint32_t out, uint32_t a_region, uint32_t b, uint32_t idesc, bool accumulate) {
+            gemm_ts<BN>(leader, out, a_region, b, idesc, accumulate);
+            if constexpr (SPLIT) gemm_ts<BN>(leader, out, a_region + 16, b, idesc_o64, true);
+          };
           if (chain == 0) {
-            gemm_ts<BN>(leader, out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o1, accum);              // ddP . V | dO
-            if (kQStat) gemm_ts<BN>(leader, out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o1, true);   // P . ddV
+            outputs(out1, acc + 1 * BN, mn_lo(sl, 2), idesc_o1, accum);              // ddP . V | dO
+            if (kQStat) outputs(out1, acc + 0 * BN, mn_lo(sl, 3), idesc_o1, true);   // P . ddV
           } else {
-            gemm_ts<BN>(leader, out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o0, accum);  // dS  . ddK | ddQ
-            gemm_ts<BN>(leader, out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o0, true);   // dS2 . K   | Q
+            outputs(out0, acc + 2 * BN, mn_lo(sl, 1), idesc_o0, accum);  // dS  . ddK | ddQ
+            outputs(out0, acc + 3 * BN, mn_lo(sl, 0), idesc_o0, true);   // dS2 . K   | Q
           }
           commit(&bars->strm_free[it % C::NSLOT]);
           // Chain 1's group A of the next tile gates the next elementwise half, while chain 2's
@@ -571,8 +636,12 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc = tmem_base + C::OUT_COLS + (PASS <= 2 ? stage * C::STAGE_COLS : 0);
-        gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + (C::stat_off(1) >> 4),
-                                               strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
+        if constexpr (SPLIT)
+          gemm_ss_split<kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + (C::stat_off(1) >> 4),
+                                                  strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
+        else
+          gemm_ss<DQK, kStatBox, C::strm_box(0)>(leader, acc + BN, stat_lo + (C::stat_off(1) >> 4),
+                                                 strm_lo + slot * kSlot16 + (C::strm_base(0) >> 4), idesc_s1, true);
         if (leader) {
           umma_commit(&bars->s_full[stage]);
           umma_commit(&bars->strm_free[slot]);
@@ -658,8 +727,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         ok = __all_sync(0xffffffffu, wait_bar(early_s(PASS) ? &bars->s_ready : &bars->s_full[0], it & 1, bars, p.status));
         if (!ok) break;
         tc_fence_after();
-        if (masked) ok = ew_half_a<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
-        else ok = ew_half_a<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
+        if (masked) ok = ew_half_a<PASS, true, F16, SPLIT>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
+        else ok = ew_half_a<PASS, false, F16, SPLIT>(acc, col_base, half * (BN / 2), c, ps, tt, &bars->s_full[0], it & 1, bars, p.status);
         if (!ok) break;
         tmem_wait_st();
         tc_fence_before();
@@ -667,8 +736,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[1], it & 1, bars, p.status));
         if (!ok) break;
         tc_fence_after();
-        if (masked) ew_half_b<PASS, true, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
-        else ew_half_b<PASS, false, F16>(acc, col_base, half * (BN / 2), c, ps, tt);
+        if (masked) ew_half_b<PASS, true, F16, SPLIT>(acc, col_base, half * (BN / 2), c, ps, tt);
+        else ew_half_b<PASS, false, F16, SPLIT>(acc, col_base, half * (BN / 2), c, ps, tt);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[1]);
@@ -738,9 +807,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
             }
           }
         };
+        // split operands: a result has 64 fp32 columns, the sum of the two 64-column halves of its accumulator
+        auto store_out_split = [&](uint32_t col0, uint16_t* base16, float mul) {
+          float* dst = reinterpret_cast<float*>(base16) +
+                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * 64 + half * 32;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t a[16], b[16];
+            if (n_iter > 0) {
+              tmem_ld16(tmem_base + lane_base + col0 + half * 32 + 16 * ch, a);
+              tmem_ld16(tmem_base + lane_base + col0 + 64 + half * 32 + 16 * ch, b);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a[j] = b[j] = 0u;
+            }
+            if (g_row < n_stat) {
+              float4* d4 = reinterpret_cast<float4*>(dst + 16 * ch);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                d4[j] = make_float4((__uint_as_float(a[4 * j]) + __uint_as_float(b[4 * j])) * mul,
+                                    (__uint_as_float(a[4 * j + 1]) + __uint_as_float(b[4 * j + 1])) * mul,
+                                    (__uint_as_float(a[4 * j + 2]) + __uint_as_float(b[4 * j + 2])) * mul,
+                                    (__uint_as_float(a[4 * j + 3]) + __uint_as_float(b[4 * j + 3])) * mul);
+            }
+          }
+        };
         // dS and dS2 were stored without the factor `scale`: it is applied to dQ2 | dK2 here
-        store_out(std::integral_constant<int, DQK>{}, 0, p.out0, c.scale);
-        store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
+        if constexpr (SPLIT) {
+          store_out_split(0, p.out0, c.scale);
+          store_out_split(C::OUT0_COLS, p.out1, 1.f);
+        } else {
+          store_out(std::integral_constant<int, DQK>{}, 0, p.out0, c.scale);
+          store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
+        }
       }
     }
   }
@@ -756,15 +856,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
 // ------------------------------------------------------------------ host side
 
-template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false>
+// fp32 -> [hi(64) | lo(64)] bf16 rows (see split_pack): one thread per pair of columns.
+__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs) {
+  const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= pairs) return;
+  const long row = i >> 5;          // 32 pairs of columns per row of 64
+  const int c2 = static_cast<int>(i & 31);
+  const float2 x = reinterpret_cast<const float2*>(src)[i];
+  uint32_t hi, lo;
+  split_pack(x.x, x.y, hi, lo);
+  dst[row * 64 + c2] = hi;          // a split row is 128 bf16 = 64 words: hi in words [0, 32), lo in [32, 64)
+  dst[row * 64 + 32 + c2] = lo;
+}
+
+template <int PASS, int DQK, int DV, int BN, int FUSED = 0, bool F16 = false, bool SPLIT = false>
 int launch(const FhobProblem& p, cudaStream_t s) {
   using C = Cfg<PASS, DQK, DV, BN>;
-  constexpr auto kernel = tc_pass_kernel<PASS, DQK, DV, BN, FUSED, F16>;
+  constexpr auto kernel = tc_pass_kernel<PASS, DQK, DV, BN, FUSED, F16, SPLIT>;
   RowVectors rv = row_vectors(p);
   TcParams tp;
   memset(&tp, 0, sizeof(tp));
   const void* q_side[3] = {p.q, p.ddq, p.d_o};
   const void* k_side[4] = {p.k, p.ddk, p.v, p.ddv};
+  if (SPLIT) {
+    // the kernels read the bf16 hi/lo copies the preparation step left behind the row vectors
+    SplitBuffers sb = split_buffers(p);
+    q_side[0] = sb.q; q_side[1] = sb.ddq; q_side[2] = sb.d_o;
+    k_side[0] = sb.k; k_side[1] = sb.ddk; k_side[2] = sb.v; k_side[3] = sb.ddv;
+  }
   int st = FHOB_OK;
   if (PASS != 4) {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
@@ -796,17 +915,17 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   return FHOB_OK;
 }
 
-template <int DQK, int DV, bool F16>
+template <int DQK, int DV, bool F16, bool SPLIT = false>
 int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
   switch (pass) {
     // pass 1 streams 128-row tiles (the stacked [K ; ddK] operand reaches N = 256), the others 64;
     // it touches no tile of the second head dim
-    case 1: return launch<1, DQK, DQK, 128, 0, F16>(p, s);
-    case 2: return launch<2, DQK, DV, 64, 0, F16>(p, s);
-    case 12: return launch<2, DQK, DV, 64, 1, F16>(p, s);  // passes 1 and 2 in one sweep
-    case 13: return launch<2, DQK, DV, 64, 2, F16>(p, s);  // the same, also producing D = sum P dP (no O given)
-    case 3: return launch<3, DQK, DV, 64, 0, F16>(p, s);
-    case 4: return launch<4, DQK, DV, 64, 0, F16>(p, s);
+    case 1: return launch<1, DQK, DQK, 128, 0, F16, SPLIT>(p, s);
+    case 2: return launch<2, DQK, DV, 64, 0, F16, SPLIT>(p, s);
+    case 12: return launch<2, DQK, DV, 64, 1, F16, SPLIT>(p, s);  // passes 1 and 2 in one sweep
+    case 13: return launch<2, DQK, DV, 64, 2, F16, SPLIT>(p, s);  // the same, also producing D = sum P dP (no O given)
+    case 3: return launch<3, DQK, DV, 64, 0, F16, SPLIT>(p, s);
+    case 4: return launch<4, DQK, DV, 64, 0, F16, SPLIT>(p, s);
   }
   return FHOB_ERR_ARG;
 }
@@ -818,15 +937,7 @@ int dispatch_dims(int pass, const FhobProblem& p, cudaStream_t s) {
   return dv == 64 ? dispatch<128, 64, F16>(pass, p, s) : dispatch<128, 128, F16>(pass, p, s);
 }
 
-}  // namespace
-
-bool tc_supported(const FhobProblem& p) {
-  const int dv = head_dim_v(p);
-  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (dv == 64 || dv == 128);
-}
-
-int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
-  if (!tc_supported(p)) return FHOB_ERR_SHAPE;
+int check_arch() {
   static thread_local int checked_dev = -1;
   int dev = 0;
   FHOB_CUDA_OK(cudaGetDevice(&dev));
@@ -836,6 +947,44 @@ int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
     if (major != 10) return FHOB_ERR_ARCH;
     checked_dev = dev;
   }
+  return FHOB_OK;
+}
+
+}  // namespace
+
+bool tc_supported(const FhobProblem& p) {
+  const int dv = head_dim_v(p);
+  if (p.dtype == FHOB_F32) return tc_split_supported(p);
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (dv == 64 || dv == 128);
+}
+
+// fp32 problems take the tensor-core path when both head dims are 64 and the workspace has room
+// for the bf16 hi/lo copies of the seven inputs (fhob_workspace_bytes_problem says how much)
+bool tc_split_supported(const FhobProblem& p) {
+  return p.dtype == FHOB_F32 && p.d == 64 && head_dim_v(p) == 64 && p.workspace &&
+         p.workspace_bytes >= split_workspace_bytes(p);
+}
+
+int tc_split_inputs(const FhobProblem& p, cudaStream_t s) {
+  if (!tc_split_supported(p)) return FHOB_ERR_SHAPE;
+  SplitBuffers sb = split_buffers(p);
+  const void* src[7] = {p.q, p.ddq, p.d_o, p.k, p.ddk, p.v, p.ddv};
+  void* dst[7] = {sb.q, sb.ddq, sb.d_o, sb.k, sb.ddk, sb.v, sb.ddv};
+  for (int i = 0; i < 7; ++i) {
+    const long rows = static_cast<long>(p.bh) * (i < 3 ? p.n_q : p.n_k);
+    const long pairs = rows * 32;
+    split_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(
+        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs);
+    FHOB_CUDA_OK(cudaGetLastError());
+  }
+  return FHOB_OK;
+}
+
+int tc_pass(int pass, const FhobProblem& p, cudaStream_t s) {
+  if (!tc_supported(p)) return FHOB_ERR_SHAPE;
+  int st = check_arch();
+  if (st != FHOB_OK) return st;
+  if (p.dtype == FHOB_F32) return dispatch<128, 128, false, true>(pass, p, s);
   return p.dtype == FHOB_F16 ? dispatch_dims<true>(pass, p, s) : dispatch_dims<false>(pass, p, s);
 }
 

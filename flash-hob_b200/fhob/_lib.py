@@ -17,6 +17,7 @@ SYMBOLS = (
     "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4", "fhob_row_stats",
     "fhob_read_status", "fhob_forward", "fhob_backward", "fhob_bwdbwd_static_scratch",
     "fhob_selftest_expired_wait", "fhob_visible_tiles", "fhob_static_scratch_status",
+    "fhob_workspace_bytes_problem",
 )
 STATIC_SCRATCH_MAX_ROWS = 262144
 
@@ -53,6 +54,8 @@ def load() -> C.CDLL:
     lib.fhob_last_cuda_error.restype = C.c_char_p
     lib.fhob_workspace_bytes.restype = C.c_size_t
     lib.fhob_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
+    lib.fhob_workspace_bytes_problem.restype = C.c_size_t
+    lib.fhob_workspace_bytes_problem.argtypes = [P]
     for name in ("fhob_bwdbwd", "fhob_prepass", "fhob_pass1", "fhob_pass2", "fhob_pass12", "fhob_pass3", "fhob_pass4",
                  "fhob_read_status", "fhob_bwdbwd_static_scratch"):
         fn = getattr(lib, name)

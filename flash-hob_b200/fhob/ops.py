@@ -95,15 +95,6 @@ class _Problem:
         self.device = dev
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         lib = _lib.load()
-        nbytes = lib.fhob_workspace_bytes(bh, n_q)
-        if workspace is None:
-            self.ws = _workspace(dev, self.stream, nbytes)
-        else:
-            if (workspace.device != dev or workspace.dtype != torch.uint8 or not workspace.is_contiguous()
-                    or workspace.numel() < nbytes or workspace.data_ptr() % 256):
-                raise ValueError(f"workspace: need a contiguous uint8 tensor of at least {nbytes} bytes on {dev}, "
-                                 "256-byte aligned")
-            self.ws = workspace
         p = _lib.FhobProblem()
         p.bh, p.n_q, p.n_k, p.d = bh, n_q, n_k, d
         p.d_v = 0 if d_v == d else d_v
@@ -112,6 +103,17 @@ class _Problem:
         p.window = _window(is_causal, window)
         p.impl = _lib.IMPL[impl]
         p.scale = float(scale)
+        if workspace is None:
+            # what lets the library take its fastest path (fp32 with head dim 64: room for the bf16
+            # hi/lo copies of the inputs, so that the problem runs on the tensor cores)
+            self.ws = _workspace(dev, self.stream, lib.fhob_workspace_bytes_problem(C.byref(p)))
+        else:
+            nbytes = lib.fhob_workspace_bytes(bh, n_q)
+            if (workspace.device != dev or workspace.dtype != torch.uint8 or not workspace.is_contiguous()
+                    or workspace.numel() < nbytes or workspace.data_ptr() % 256):
+                raise ValueError(f"workspace: need a contiguous uint8 tensor of at least {nbytes} bytes on {dev}, "
+                                 "256-byte aligned")
+            self.ws = workspace
         p.q, p.k, p.v, p.o, p.d_o = (t.data_ptr() for t in (q, k, v, o, do))
         if no_o:
             p.o = None
@@ -163,7 +165,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     Same positional signature and return order as the reference
     (fhog/triton_bwdbwd.py:558, :648).  Tensors are ``(BH, N, D)`` like the
     reference or ``(B, H, N, D)``; bfloat16 or float16 (tensor-core kernels,
-    fp32 accumulation) or float32 (CUDA-core kernels).  ``V``, ``O``, ``dO``
+    fp32 accumulation) or float32 (tensor cores with every operand split into
+    a bf16 hi + lo pair when D = 64, CUDA-core kernels otherwise).  ``V``, ``O``, ``dO``
     and ``ddV`` may have a head dim of their own (the reference operator has a
     single D, :577; its maths does not need that, jax_refs/flash_impl.py:381-389):
     ``dV2`` and ``ddO`` then have it too; the tensor-core kernels take head dims

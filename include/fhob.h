@@ -30,9 +30,11 @@ extern "C" {
 /* FHOB_F16: the reference's benchmark dtype (fhog/benchhhh.py:19); tensor-core path like bf16 */
 enum { FHOB_BF16 = 0, FHOB_F32 = 1, FHOB_F16 = 2 };
 
-/* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for bf16,
- * fp32 CUDA-core kernels for fp32.  SIMT forces the CUDA-core kernels for
- * either type (debugging aid; same four passes, same row statistics). */
+/* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for 16-bit
+ * elements (head dims 64 or 128) and for fp32 with both head dims 64 when the
+ * workspace has fhob_workspace_bytes_problem() bytes; CUDA-core kernels for
+ * everything else.  SIMT forces the CUDA-core kernels for any type
+ * (debugging aid; same four passes, same row statistics). */
 enum { FHOB_IMPL_AUTO = 0, FHOB_IMPL_SIMT = 1, FHOB_IMPL_TCGEN05 = 2 };
 
 /* Status codes.  Device-side conditions are accumulated (OR-ed) into the
@@ -113,6 +115,20 @@ const char* fhob_last_cuda_error(void);
  * (fhog/triton_bwdbwd.py:580-584).
  */
 size_t fhob_workspace_bytes(int32_t bh, int32_t n_q);
+
+/*
+ * Bytes of scratch that let the library take its fastest path for this
+ * particular problem (reads bh, n_q, n_k, d, d_v, dtype, impl).  Equal to
+ * fhob_workspace_bytes(bh, n_q) except for fp32 problems with both head dims
+ * 64: those run on the tensor cores (every fp32 operand as a bf16 hi + lo
+ * pair, three products per contraction, fp32 accumulation) if the workspace
+ * also has room for the bf16 copies of the seven inputs (their size again:
+ * still linear in the sequence lengths).  With a smaller workspace such a
+ * problem runs on the CUDA-core kernels (impl AUTO) or is refused with
+ * FHOB_ERR_WORKSPACE (impl TCGEN05).  The reference has no counterpart: its
+ * Triton kernels take whatever precision tl.dot gives fp32 inputs.
+ */
+size_t fhob_workspace_bytes_problem(const FhobProblem* p);
 
 /*
  * The whole operator: row-statistics pre-pass and the recomputation

@@ -64,13 +64,87 @@ SMALL = [(2, 128, 128, 64), (2, 128, 256, 64), (1, 256, 128, 128), (3, 96, 160, 
 @pytest.mark.parametrize("bh,nq,nk,d", SMALL)
 def test_fp32_cuda_core_path(bh, nq, nk, d, causal):
     x = make_inputs(bh, nq, nk, d, seed=21, dtype=torch.float64)
-    got, ref, _ = _run(x, d ** -0.5, causal, torch.float32, "auto")
+    got, ref, _ = _run(x, d ** -0.5, causal, torch.float32, "simt")
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert O.rel_err(g, r) < TOL_F32, n
 
 
-def test_fp32_config_one():
-    """B=1 H=2 N=256 D=64 non-causal fp32, 4-D layout, against grad-of-grad (form A)."""
+FP32_TC_CASES = [(2, 128, 128, False, None), (2, 256, 384, False, None), (2, 384, 256, True, None),
+                 (3, 200, 328, True, None), (1, 99, 131, False, None), (2, 320, 320, True, 70), (1, 1, 300, False, None)]
+
+
+@pytest.mark.parametrize("bh,nq,nk,causal,window", FP32_TC_CASES)
+def test_fp32_tensor_core_path(bh, nq, nk, causal, window):
+    """fp32 problems with head dim 64 on the tensor cores: every operand as a bf16 hi + lo pair,
+    three products per contraction, fp32 accumulation.  Same 1e-4 bound as the CUDA-core path,
+    for the four results, the row statistics (both the two-pass and the one-sweep form) and the
+    call without the saved output."""
+    import fhob
+    import math
+    wl = math.inf if window is None else window
+    x = make_inputs(bh, nq, nk, 64, seed=23, dtype=torch.float64)
+    scale = 0.125
+    if causal and nk < nq and window is None:
+        ref, lse, o, stats = _oracle(x, scale, causal)
+    else:
+        ref = O.bwdbwd_closed_form(*x.values(), scale, causal, sliding_window_length=wl)
+        lse = O.attn_lse(x["q"], x["k"], scale, causal, sliding_window_length=wl)
+        o = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal, sliding_window_length=wl)
+        stats = O.bwdbwd_row_stats(*x.values(), scale, causal) if window is None else None
+    dev = {k: v.float().cuda() for k, v in x.items()}
+    args = (dev["q"], dev["k"], dev["v"], o.float().cuda(), dev["do"], dev["ddq"], dev["ddk"], dev["ddv"],
+            lse.float().cuda(), scale)
+    kw = dict(is_causal=causal, sliding_window=window, impl="tcgen05")
+    got = fhob.flash_bwdbwd(*args, check=True, **kw)
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert g.dtype == torch.float32 and O.rel_err(g, r) < TOL_F32, n
+    again = fhob.flash_bwdbwd(*args, check=True, **kw)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b)                      # bit-exact run to run
+    auto = fhob.flash_bwdbwd(*args, check=True, **dict(kw, impl="auto"))
+    for a, b in zip(got, auto):
+        assert torch.equal(a, b)                      # AUTO takes the same path when the workspace has the room
+    got = fhob.flash_bwdbwd(*args[:3], None, *args[4:], check=True, **kw)      # D from the sweep
+    for n, g, r in zip(OUT_NAMES, got, ref):
+        assert O.rel_err(g, r) < TOL_F32, n
+    if stats is not None:
+        for fused in (False, True):
+            res = fhob.run_passes(*args, is_causal=causal, impl="tcgen05", upto=2, fused12=fused)
+            assert res["status"] == 0
+            for n, r in zip(("d", "dd", "b"), stats):
+                assert O.rel_err(res[n], r) < TOL_F32, (n, fused)
+
+
+def test_fp32_tensor_core_path_needs_head_dim_64_and_a_larger_workspace():
+    import fhob
+    from fhob import _lib
+    import ctypes as C
+    x = make_inputs(2, 128, 128, 128, seed=25, dtype=torch.float32, device="cuda")
+    L = torch.zeros(2, 128, device="cuda")
+    with pytest.raises(RuntimeError, match="shape not supported"):
+        fhob.flash_bwdbwd(x["q"], x["k"], x["v"], x["q"], x["do"], x["ddq"], x["ddk"], x["ddv"], L, 0.1, impl="tcgen05")
+    x = make_inputs(2, 128, 256, 64, seed=25, dtype=torch.float32, device="cuda")
+    lib = _lib.load()
+    small = torch.empty(lib.fhob_workspace_bytes(2, 128), dtype=torch.uint8, device="cuda")
+    p = _lib.FhobProblem()
+    p.bh, p.n_q, p.n_k, p.d, p.dtype = 2, 128, 256, 64, _lib.FHOB_F32
+    assert lib.fhob_workspace_bytes_problem(C.byref(p)) >= small.numel() + (3 * 128 + 4 * 256) * 2 * 256
+    with pytest.raises(RuntimeError, match="workspace"):
+        fhob.flash_bwdbwd(x["q"], x["k"], x["v"], x["q"], x["do"], x["ddq"], x["ddk"], x["ddv"], L, 0.125,
+                          impl="tcgen05", workspace=small)
+    # AUTO with the small workspace: the CUDA-core kernels, same results to the fp32 bound
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 0.125)
+    args = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 0.125)
+    a = fhob.flash_bwdbwd(*args, workspace=small, check=True)
+    b = fhob.flash_bwdbwd(*args, check=True)
+    for u, v in zip(a, b):
+        assert O.rel_err(u, v) < TOL_F32 and not torch.equal(u, v)      # two different kernel families
+
+
+@pytest.mark.parametrize("impl", ["auto", "simt"])
+def test_fp32_config_one(impl):
+    """B=1 H=2 N=256 D=64 non-causal fp32, 4-D layout, against grad-of-grad (form A); `auto` runs it
+    on the tensor cores (split operands), `simt` on CUDA cores."""
     import fhob
     x = make_inputs(2, 256, 256, 64, seed=1234, dtype=torch.float64)
     ref = O.bwdbwd_autograd(*x.values(), 0.125, False)
@@ -79,7 +153,7 @@ def test_fp32_config_one():
     dev = {k: v.float().cuda().reshape(1, 2, 256, 64) for k, v in x.items()}
     got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o.float().cuda().reshape(1, 2, 256, 64), dev["do"],
                             dev["ddq"], dev["ddk"], dev["ddv"], lse.float().cuda().reshape(1, 2, 256), 0.125,
-                            check=True)
+                            check=True, impl=impl)
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert g.shape == (1, 2, 256, 64)
         assert O.rel_err(g.reshape(2, 256, 64), r) < TOL_F32, n
