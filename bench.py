@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the double-backward flash attention operator.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl fhob|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl fhob|reference|reference-triton]
 
 One "step" is one call of the operator (pre-pass + three sweeps) over this
 rank's heads of the job, resident in HBM.  The default job is the multi-GPU
@@ -52,9 +52,14 @@ WORKLOADS = {
                  desc="bf16 causal B=1 H=32 N=32768 D=128"),
     "n8192": dict(bh=32, n_q=8192, n_k=8192, d=128, causal=False, cot=1.0,
                   desc="bf16 non-causal B=1 H=32 N=8192 D=128"),
+    "cfg1": dict(bh=2, n_q=256, n_k=256, d=64, causal=False, cot=1.0, dtype="f32",
+                 desc="fp32 non-causal B=1 H=2 N=256 D=64 (the reference's CPU-runnable case; launch-latency-bound)"),
+    "f32-n2048": dict(bh=64, n_q=2048, n_k=2048, d=64, causal=False, cot=1.0, dtype="f32",
+                      desc="fp32 non-causal 64 heads N=2048 D=64 (cfg2's shape in fp32: tensor cores with split "
+                           "bf16 operands, three products per contraction)"),
 }
 # the other configurations carried by the one-GPU line: (workload, heads, steps)
-EXTRAS = (("cfg2", 64, 20), ("cfg3", 128, 8), ("cfg4", 4, 5), ("n8192", 32, 5))
+EXTRAS = (("cfg2", 64, 20), ("cfg3", 128, 8), ("cfg4", 4, 5), ("n8192", 32, 5), ("cfg1", 2, 20), ("f32-n2048", 64, 5))
 GEMM_UNITS = {"pass12": 5, "pass3": 9, "pass4": 8}
 EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass at N_Q=4096,
@@ -168,7 +173,8 @@ class ClockSampler:
 def make_batch(w, heads, device, seed):
     g = torch.Generator(device=device).manual_seed(seed)
     def rnd(n, s=1.0):
-        return (torch.randn(heads, n, w["d"], generator=g, device=device, dtype=torch.float32) * s).bfloat16()
+        t = (torch.randn(heads, n, w["d"], generator=g, device=device, dtype=torch.float32) * s).bfloat16()
+        return t.float() if w.get("dtype") == "f32" else t   # fp32 workloads: bf16-representable fp32 values
     return dict(q=rnd(w["n_q"]), k=rnd(w["n_k"]), v=rnd(w["n_k"]), do=rnd(w["n_q"], w["cot"]),
                 ddq=rnd(w["n_q"], w["cot"]), ddk=rnd(w["n_k"], w["cot"]), ddv=rnd(w["n_k"], w["cot"]))
 
@@ -231,12 +237,12 @@ class Case:
         self.o, self.lse = fhob.attention_forward(x["q"], x["k"], x["v"], self.scale, is_causal=w["causal"])
         self.args = (x["q"], x["k"], x["v"], self.o, x["do"], x["ddq"], x["ddk"], x["ddv"], self.lse, self.scale)
         self.in_bytes = sum(t.numel() * t.element_size() for t in self.args[:9])
-        self.out_bytes = 2 * (x["q"].numel() + x["k"].numel()) * 2
+        self.out_bytes = 2 * (x["q"].numel() + x["k"].numel()) * x["q"].element_size()
         self.unit_flops = 2.0 * heads * pairs(w) * w["d"]
 
-    def step(self):
+    def step(self, impl="auto"):
         import fhob
-        return fhob.flash_bwdbwd(*self.args, is_causal=self.w["causal"])
+        return fhob.flash_bwdbwd(*self.args, is_causal=self.w["causal"], impl=impl)
 
     def status(self):
         from fhob.ops import _Problem
@@ -318,6 +324,21 @@ def run_extra(name, heads, steps, dev):
     res.update({k: round(v, 4) for k, v in summarise(w, heads, ms).items()})
     res["passes"] = case.time_passes(max(3, steps // 2))
     res["max_rel_err_vs_fp64_oracle"] = case.check_head(outs, heads - 1)
+    if w.get("dtype") == "f32":
+        # every contraction is issued as three bf16 products (hi.hi + hi.lo + lo.hi): the executed-flop
+        # figures above count each contraction once, the tensor pipe does three times that
+        res["dtype"] = "f32"
+        res["tolerance"] = 1e-4
+        res["products_per_contraction"] = 3
+        case.step("simt")
+        torch.cuda.synchronize()
+        e0.record()
+        outs = case.step("simt")
+        e1.record()
+        torch.cuda.synchronize()
+        res["cuda_core_kernels"] = dict(ms_per_step=round(e0.elapsed_time(e1), 4),
+                                        tflops_alg=round(f_alg(w, heads) / e0.elapsed_time(e1) / 1e9, 2),
+                                        max_rel_err_vs_fp64_oracle=case.check_head(outs, heads - 1))
     return res
 
 
@@ -373,8 +394,13 @@ def competitor_child(args):
     torch.cuda.set_device(dev)
     w = dict(WORKLOADS[args.workload])
     heads = args.heads or w["bh"]
-    assert not w["causal"]
-    case = Case(w, heads, dev, seed=777)
+    if w["causal"] or w.get("dtype") == "f32":
+        print(json.dumps(dict(error="the reference operator has no causal mask and is benchmarked in 16-bit only")))
+        return
+    # its autotune key holds the sequence lengths and the head dim, not the number of heads, so the
+    # (slow) tuning runs are made on a 16-head case
+    tune_heads = min(heads, 16)
+    case = Case(w, tune_heads, dev, seed=777)
     t0 = time.time()
     from fhog.triton_bwdbwd import bwdbwd_kernel_stage1, bwdbwd_kernel_stage2, flash_bwdbwd as ref_bwdbwd
     how = "as shipped: fhog.flash_bwdbwd, a torch.compile(fullgraph=True) wrapper around two autotuned Triton kernels"
@@ -398,6 +424,10 @@ def competitor_child(args):
         theirs = ref_bwdbwd(*case.args)
     torch.cuda.synchronize()
     setup_s = time.time() - t0
+    if tune_heads < heads:
+        del theirs, case
+        torch.cuda.empty_cache()
+        case = Case(w, heads, dev, seed=777)
     for _ in range(2):
         theirs = ref_bwdbwd(*case.args)
     torch.cuda.synchronize()
@@ -462,7 +492,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default="cfg5", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="fhob", choices=["fhob", "reference"])
+    ap.add_argument("--impl", default="fhob", choices=["fhob", "reference", "reference-triton"],
+                    help="reference: the CPU arm (oracle port on the host cores); reference-triton: the reference's "
+                         "own Triton operator on one GPU, same workload (non-causal 16-bit workloads only)")
     ap.add_argument("--heads", type=int, default=0, help="heads of the whole job (default: the workload's); "
                     "smaller values give the small cases profiler captures need")
     ap.add_argument("--min-timed-s", type=float, default=1.0,
@@ -491,6 +523,21 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, rank)
+        return
+    if args.impl == "reference-triton":
+        if rank == 0:
+            heads = w["bh"] // max(1, args.gpus)
+            res = competitor_triton(((args.workload, heads),), steps=max(2, min(args.steps, 10)),
+                                    timeout_s=max(args.competitor_timeout, 600))[args.workload]
+            cfg = config_block(args.workload, w, heads, 1)
+            cfg["sample"] = f"{heads} heads on one GPU (one rank's share when --gpus > 1)"
+            if "error" in res:
+                emit(dict(impl="reference-triton", unavailable=res["error"], config=cfg))
+            else:
+                t = res["reference_triton"]
+                emit(dict(metric=METRIC, value=t["tflops_alg"], unit="TFLOP/s", impl="reference-triton", n_gpus=1,
+                          steps=res["steps"], warmup=2, ms_per_step=t["ms_per_step"], higher_is_better=True,
+                          scaling="strong", vs_baseline=None, dtype="bf16", data="synthetic", config=cfg, detail=res))
         return
 
     import torch.distributed as dist
