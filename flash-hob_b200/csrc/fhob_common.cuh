@@ -135,7 +135,9 @@ int simt_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream
 // tcgen05 / TMEM / TMA kernels (bf16, d in {64,128}): tc_kernels.cu
 bool tc_supported(const FhobProblem& p);
 bool tc_split_supported(const FhobProblem& p);            // fp32 on the tensor cores (split operands)
-int tc_split_inputs(const FhobProblem& p, cudaStream_t s);  // writes the hi/lo copies into the workspace
+// which inputs tc_split_inputs copies (the operator needs all seven, the forward q, k, v, ...)
+enum { kSplitQ = 1, kSplitDDQ = 2, kSplitDO = 4, kSplitK = 8, kSplitDDK = 16, kSplitV = 32, kSplitDDV = 64, kSplitAll = 127 };
+int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which = kSplitAll);  // writes hi/lo copies into the workspace
 int tc_pass(int pass, const FhobProblem& p, cudaStream_t s);
 
 // tensor-core forward (O, L) and first backward (dQ, dK, dV): tc_first_order.cu

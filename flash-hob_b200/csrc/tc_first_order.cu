@@ -20,6 +20,8 @@
 //   BQ   (queries stationary,  64 keys per tile): dS = P (dP - D), dP = dO V^T;  dQ += dS K
 //   BK   (keys stationary,  64 queries per tile): transposed tiles;  dV += P^T dO, dK += dS^T Q
 // The backward follows jax_refs/flash_impl.py:124-173 with P = exp(S - L) and D = rowsum(dO * O).
+#include <type_traits>
+
 #include "tc_common.cuh"
 
 namespace fhob {
@@ -28,29 +30,37 @@ namespace {
 enum { FO_LSE = 0, FO_BQ = 2, FO_BK = 3, FO_ONE = 4 };
 constexpr int FO_TAIL = 3072;  // barriers, TMEM base, abort flag, (max, sum) exchange
 
-template <int MODE, int D>
+// Two head dims: the first stationary and the first streamed tile of every mode are q/k-side
+// tensors (DQK columns), the second ones v-side tensors (DV columns):
+//   ONE: Q | K, V     LSE: Q | K     BQ: Q, dO | K, V     BK: K, V | Q, dO
+template <int MODE, int DQK, int DV>
 struct FoCfg {
   static constexpr bool kQStat = MODE != FO_BK;
   static constexpr bool kForward = MODE == FO_LSE || MODE == FO_ONE;
   static constexpr int BN = kForward ? 128 : 64;
-  static constexpr int NSTAT = kForward ? 1 : 2;         // Q | Q | Q, dO | K, V
-  static constexpr int NSTRM = MODE == FO_LSE ? 1 : 2;   // K | K, V | K, V | Q, dO
+  static constexpr int NSTAT = kForward ? 1 : 2;
+  static constexpr int NSTRM = MODE == FO_LSE ? 1 : 2;
   static constexpr int NACC = kForward ? 1 : 2;          // score tiles of a stage: S | S | S, dP | S^T, dP^T
   static constexpr int NOUT = MODE == FO_LSE ? 0 : (MODE == FO_BK ? 2 : 1);
-  static constexpr int OUT_COLS = NOUT * D;
+  __host__ __device__ static constexpr int tile_d(int i) { return i == 0 ? DQK : DV; }
+  static constexpr int OUT0_COLS = NOUT == 0 ? 0 : (MODE == FO_ONE ? DV : DQK);   // O | dQ | dK
+  static constexpr int OUT1_COLS = NOUT == 2 ? DV : 0;                            // dV
+  static constexpr int OUT_COLS = OUT0_COLS + OUT1_COLS;
   static constexpr int STAGE_COLS = NACC * BN;
-  static constexpr int STAT_BYTES = BM * D * 2;
-  static constexpr int STRM_BYTES = BN * D * 2;
+  __host__ __device__ static constexpr int stat_off(int i) { return i == 0 ? 0 : stat_off(i - 1) + BM * tile_d(i - 1) * 2; }
+  __host__ __device__ static constexpr int strm_off(int i) { return i == 0 ? 0 : strm_off(i - 1) + BN * tile_d(i - 1) * 2; }
+  static constexpr int STAT_BYTES = stat_off(NSTAT);
+  static constexpr int STRM_BYTES = strm_off(NSTRM);
   // BK: -L*log2e and -D of the streamed queries travel with the slot
   static constexpr int VEC_BYTES = MODE == FO_BK ? 2 * BN * 4 : 0;
-  static constexpr int TX_BYTES = NSTRM * STRM_BYTES + VEC_BYTES;
-  static constexpr int SLOT_BYTES = NSTRM * STRM_BYTES + (VEC_BYTES ? 1024 : 0);  // tiles stay 1024-byte aligned
-  static constexpr int NSLOT_FIT = (SMEM_LIMIT - FO_TAIL - NSTAT * STAT_BYTES) / SLOT_BYTES;
+  static constexpr int TX_BYTES = STRM_BYTES + VEC_BYTES;
+  static constexpr int SLOT_BYTES = STRM_BYTES + (VEC_BYTES ? 1024 : 0);  // tiles stay 1024-byte aligned
+  static constexpr int NSLOT_FIT = (SMEM_LIMIT - FO_TAIL - STAT_BYTES) / SLOT_BYTES;
   static constexpr int NSLOT = NSLOT_FIT > 4 ? 4 : NSLOT_FIT;
-  static constexpr int SMEM_BYTES = NSTAT * STAT_BYTES + NSLOT * SLOT_BYTES + FO_TAIL;
+  static constexpr int SMEM_BYTES = STAT_BYTES + NSLOT * SLOT_BYTES + FO_TAIL;
   static_assert(OUT_COLS + 2 * STAGE_COLS <= TMEM_COLS, "TMEM budget");
   static_assert(NSLOT >= 2, "need two streamed slots");
-  static_assert(D == 64 || D == 128, "head dim");
+  static_assert((DQK == 64 || DQK == 128) && (DV == 64 || DV == 128), "head dims");
 };
 
 struct FoParams {
@@ -84,15 +94,38 @@ struct FoBars {
 };
 static_assert(sizeof(FoBars) <= FO_TAIL, "tail");
 
-template <int MODE, int D, bool F16>
+// fp32 problems (SPLIT): the split-operand scheme of the double-backward kernels (tc_kernels.cu):
+// every fp32 operand as bf16 hi + lo, rows [hi(64) | lo(64)] = the two boxes of a 128-wide tile,
+// three products per contraction, 16-bit tiles handed back as hi and lo halves, the two halves
+// of an output accumulator added in the epilogue.  Head dims 64, instantiated as 128/128.
+__device__ __forceinline__ void fo_split_pack(float x, float y, uint32_t& hi, uint32_t& lo) {
+  hi = pack_bf16(x, y);
+  lo = pack_bf16(x - __uint_as_float(hi << 16), y - __uint_as_float(hi & 0xffff0000u));
+}
+
+template <int A_BOX, int B_BOX>
+__device__ __forceinline__ void fo_gemm_ss_split(bool leader, uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                                 uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int term = 0; term < 3; ++term) {   // (hi, hi), (hi, lo), (lo, hi)
+    const int ab = term == 2 ? 1 : 0, bb = term == 1 ? 1 : 0;
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks)
+      umma_ss_split(d_tmem, a_lo + ((ab * A_BOX + ks * 32) >> 4), b_lo + ((bb * B_BOX + ks * 32) >> 4), kDescHi, idesc,
+                    (accumulate || term > 0 || ks > 0) ? 1u : 0u, leader);
+  }
+}
+
+template <int MODE, int DQK, int DV, bool F16, bool SPLIT = false>
 __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__ FoParams p) {
-  using C = FoCfg<MODE, D>;
+  using C = FoCfg<MODE, DQK, DV>;
+  static_assert(!SPLIT || (DQK == 128 && DV == 128 && !F16), "split fp32 operands are [hi(64) | lo(64)] bf16 rows");
   constexpr bool kQStat = C::kQStat;
   constexpr int BN = C::BN;
   constexpr int CPT = BN / 2;  // fp32 columns of a score tile per elementwise thread
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* stat_tiles = smem;
-  uint8_t* strm_tiles = smem + C::NSTAT * C::STAT_BYTES;
+  uint8_t* strm_tiles = smem + C::STAT_BYTES;
   FoBars* bars = reinterpret_cast<FoBars*>(strm_tiles + C::NSLOT * C::SLOT_BYTES);
   int* status = p.status;
 
@@ -147,10 +180,11 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
   if (warp == TMA_WARP) {
     // ================================================= TMA producer
     if (lane == 0 && n_iter > 0) {
-      mbar_arrive_expect_tx(&bars->stat_full, C::NSTAT * C::STAT_BYTES);
+      mbar_arrive_expect_tx(&bars->stat_full, C::STAT_BYTES);
+#pragma unroll
       for (int i = 0; i < C::NSTAT; ++i)
-        for (int bx = 0; bx < D / 64; ++bx)
-          tma_load_3d(stat_tiles + i * C::STAT_BYTES + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
+        for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
+          tma_load_3d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
                       head);
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
@@ -159,13 +193,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         mbar_arrive_expect_tx(&bars->strm_full[slot], C::TX_BYTES);
         uint8_t* dst = strm_tiles + slot * C::SLOT_BYTES;
         const int n0 = (t_begin + it) * BN;
+#pragma unroll
         for (int i = 0; i < C::NSTRM; ++i)
-          for (int bx = 0; bx < D / 64; ++bx)
-            tma_load_3d(dst + i * C::STRM_BYTES + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
+          for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
+            tma_load_3d(dst + C::strm_off(i) + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
                         head);
         if (MODE == FO_BK) {
           const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
-          uint8_t* sv = dst + C::NSTRM * C::STRM_BYTES;
+          uint8_t* sv = dst + C::STRM_BYTES;
           bulk_load(sv, p.nlc + vo, BN * 4, &bars->strm_full[slot]);
           bulk_load(sv + BN * 4, p.k1 + vo, BN * 4, &bars->strm_full[slot]);
         }
@@ -203,15 +238,30 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         if (leader) umma_commit(bar);
       };
       constexpr uint32_t idesc_s = umma_idesc_bf16(BM, BN, false, false, F16);
-      constexpr uint32_t idesc_o = umma_idesc_bf16(BM, D, false, true, F16);
+      constexpr uint32_t idesc_o0 = umma_idesc_bf16(BM, C::OUT0_COLS ? C::OUT0_COLS : 64, false, true, F16);  // O | dQ | dK
+      constexpr uint32_t idesc_o1 = umma_idesc_bf16(BM, DV, false, true, F16);                                // dV
+      constexpr uint32_t idesc_o64 = umma_idesc_bf16(BM, 64, false, true, F16);   // split operands: the hi box alone
       constexpr int kStatBox = BM * 128, kStrmBox = BN * 128;
+      constexpr int kLoTile = BN / 4;   // split 16-bit tiles: the lo half starts this many columns after the hi half
       const uint32_t stat_lo = umma_desc_lo(smem_u32(stat_tiles), 16);
       const uint32_t strm_lo = umma_desc_lo(smem_u32(strm_tiles), 16);
-      constexpr uint32_t kStat16 = C::STAT_BYTES >> 4, kSlot16 = C::SLOT_BYTES >> 4, kStrm16 = C::STRM_BYTES >> 4;
+      constexpr uint32_t kStat16 = C::stat_off(1) >> 4, kSlot16 = C::SLOT_BYTES >> 4, kStrm16 = C::strm_off(1) >> 4;
       // MN-major view of streamed tile i: leading byte offset = distance between its two 64-column boxes
       auto mn_lo = [&](uint32_t slot_lo, int i) {
         return slot_lo - (1u << 16) + i * kStrm16 + (static_cast<uint32_t>(kStrmBox >> 4) << 16);
       };
+      // score product over KD columns (or over the hi/lo boxes of split operands)
+      auto scores_mma = [&](auto kd, uint32_t d, uint32_t a, uint32_t b, bool accumulate) {
+        if constexpr (SPLIT) fo_gemm_ss_split<kStatBox, kStrmBox>(leader, d, a, b, idesc_s, accumulate);
+        else gemm_ss<decltype(kd)::value, kStatBox, kStrmBox>(leader, d, a, b, idesc_s, accumulate);
+      };
+      // output product, A = 16-bit tile in TMEM; split operands: A_hi . [B_hi | B_lo], then A_lo . B_hi
+      auto outputs_mma = [&](uint32_t out, uint32_t a_region, uint32_t b, uint32_t idesc, bool accumulate) {
+        gemm_ts<BN>(leader, out, a_region, b, idesc, accumulate);
+        if constexpr (SPLIT) gemm_ts<BN>(leader, out, a_region + kLoTile, b, idesc_o64, true);
+      };
+      using KQ = std::integral_constant<int, DQK>;
+      using KV = std::integral_constant<int, DV>;
       bool ok = wait_all(&bars->stat_full, 0);
 
       if (kSplitOutputs) {
@@ -224,13 +274,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             ok = ok && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
             if (!ok) break;
             tc_fence_after();
-            gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);  // S
+            scores_mma(KQ{}, acc, stat_lo, sl, false);  // S
             commit(&bars->s_full[stage]);
           } else {
             ok = wait_all(&bars->p_full[stage], (it >> 1) & 1) && wait_all(&bars->strm_full[slot], (it / C::NSLOT) & 1);
             if (!ok) break;
             tc_fence_after();
-            gemm_ts<BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, it > 0);  // O += P . V
+            outputs_mma(tmem_base, acc, mn_lo(sl, 1), idesc_o0, it > 0);  // O += P . V
             commit(&bars->strm_free[slot]);
             if (MODE == FO_ONE) commit(&bars->o_done);
             if (leader) mbar_arrive(&bars->go[stage]);
@@ -245,7 +295,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           tc_fence_after();
           const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
           const uint32_t sl = strm_lo + slot * kSlot16;
-          gemm_ss<D, kStatBox, kStrmBox>(leader, acc + BN, stat_lo + kStat16, sl + kStrm16, idesc_s, false);  // dP
+          scores_mma(KV{}, acc + BN, stat_lo + kStat16, sl + kStrm16, false);  // dP
           commit(&bars->s_full[stage]);
         }
       } else {
@@ -256,7 +306,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           tc_fence_after();
           const uint32_t acc = tmem_base + C::OUT_COLS + stage * C::STAGE_COLS;
           const uint32_t sl = strm_lo + slot * kSlot16;
-          gemm_ss<D, kStatBox, kStrmBox>(leader, acc, stat_lo, sl, idesc_s, false);  // S
+          scores_mma(KQ{}, acc, stat_lo, sl, false);  // S
           commit(&bars->s_full[stage]);
           if (MODE == FO_LSE) commit(&bars->strm_free[slot]);
           return true;
@@ -277,13 +327,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             const uint32_t sl = strm_lo + slot * kSlot16;
             const bool accum = it > 0;
             if (MODE == FO_ONE) {
-              gemm_ts<BN>(leader, tmem_base, acc, mn_lo(sl, 1), idesc_o, accum);            // O  += P . V
+              outputs_mma(tmem_base, acc, mn_lo(sl, 1), idesc_o0, accum);                     // O  += P . V
               commit(&bars->o_done);
             } else if (MODE == FO_BQ) {
-              gemm_ts<BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dQ += dS . K
+              outputs_mma(tmem_base, acc + BN, mn_lo(sl, 0), idesc_o0, accum);                // dQ += dS . K
             } else {
-              gemm_ts<BN>(leader, tmem_base + D, acc, mn_lo(sl, 1), idesc_o, accum);        // dV += P^T . dO
-              gemm_ts<BN>(leader, tmem_base, acc + BN, mn_lo(sl, 0), idesc_o, accum);       // dK += dS^T . Q
+              outputs_mma(tmem_base + C::OUT0_COLS, acc, mn_lo(sl, 1), idesc_o1, accum);      // dV += P^T . dO
+              outputs_mma(tmem_base, acc + BN, mn_lo(sl, 0), idesc_o0, accum);                // dK += dS^T . Q
             }
             commit(&bars->strm_free[slot]);
             if (C::NACC == 2 && leader) mbar_arrive(&bars->go[stage]);
@@ -351,7 +401,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         const int slot = it % C::NSLOT;
         ok = __all_sync(0xffffffffu, wait_bar(&bars->strm_full[slot], (it / C::NSLOT) & 1, bars, status));
         if (!ok) break;
-        sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::NSTRM * C::STRM_BYTES) + half * CPT * 4;
+        sv = smem_u32(strm_tiles + slot * C::SLOT_BYTES + C::STRM_BYTES) + half * CPT * 4;
       }
       ok = __all_sync(0xffffffffu, wait_bar(&bars->s_full[stage], (it >> 1) & 1, bars, status));
       if (!ok) break;
@@ -393,7 +443,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         // single-sweep forward: online softmax with a lazily updated reference maximum.  P is
         // formed against m_used, which follows the running row maximum only when that has grown
         // by more than 8 (P stays below 2^8); O and the row sum are rescaled on those occasions.
-        uint32_t xx[2][32], w[2][16];
+        uint32_t xx[2][32], w[2][16], w_lo[2][16];
         tmem_ld32(acc, xx[0]);
         tmem_ld32(acc + 32, xx[1]);
         tmem_wait_ld();
@@ -427,9 +477,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           tc_fence_after();
           const float alpha = (need && run_m != -INFINITY) ? ex2(run_m - tile_m) : 1.f;
 #pragma unroll
-          for (int ch = 0; ch < D / 64; ++ch) {
+          for (int ch = 0; ch < C::OUT0_COLS / 64; ++ch) {
             uint32_t v[32], lo16[16], hi16[16];
-            const uint32_t addr = tmem_base + lane_base + half * (D / 2) + 32 * ch;
+            const uint32_t addr = tmem_base + lane_base + half * (C::OUT0_COLS / 2) + 32 * ch;
             tmem_ld32(addr, v);
             tmem_wait_ld();
 #pragma unroll
@@ -453,16 +503,22 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
             const float2 d = __fadd2_rn(f2(xx[c][j], xx[c][j + 1]), make_float2(neg_m, neg_m));
             const float2 pr = make_float2(ex2(d.x), ex2(d.y));
             sum = __fadd2_rn(sum, pr);
-            w[c][j / 2] = pack16<F16>(pr.x, pr.y);
+            if constexpr (SPLIT) fo_split_pack(pr.x, pr.y, w[c][j / 2], w_lo[c][j / 2]);
+            else w[c][j / 2] = pack16<F16>(pr.x, pr.y);
           }
         run_l += sum.x + sum.y;
+        // the thread's 64 score columns take its 32 packed columns of P (split: then 32 of the lo halves)
         tmem_st16(acc, w[0]);
         tmem_st16(acc + 16, w[1]);
+        if constexpr (SPLIT) {
+          tmem_st16(acc + 32, w_lo[0]);
+          tmem_st16(acc + 48, w_lo[1]);
+        }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[stage]);
       } else {
-        uint32_t s[32], dp[32], w_p[16], w_ds[16];
+        uint32_t s[32], dp[32], w_p[16], w_ds[16], w_p_lo[16], w_ds_lo[16];
         tmem_ld32(acc, s);
         tmem_ld32(acc + BN, dp);
         tmem_wait_ld();
@@ -490,12 +546,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
               pr.x = ok0 ? pr.x : 0.f; pr.y = ok1 ? pr.y : 0.f;
               ds.x = ok0 ? ds.x : 0.f; ds.y = ok1 ? ds.y : 0.f;
             }
-            w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
-            if (MODE == FO_BK) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
+            if constexpr (SPLIT) {
+              fo_split_pack(ds.x, ds.y, w_ds[j / 2], w_ds_lo[j / 2]);
+              if (MODE == FO_BK) fo_split_pack(pr.x, pr.y, w_p[j / 2], w_p_lo[j / 2]);
+            } else {
+              w_ds[j / 2] = pack16<F16>(ds.x, ds.y);
+              if (MODE == FO_BK) w_p[j / 2] = pack16<F16>(pr.x, pr.y);
+            }
           }
         }
         tmem_st16(acc + BN, w_ds);
         if (MODE == FO_BK) tmem_st16(acc, w_p);
+        if constexpr (SPLIT) {
+          tmem_st16(acc + BN + 16, w_ds_lo);
+          if (MODE == FO_BK) tmem_st16(acc + 16, w_p_lo);
+        }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&bars->p_full[stage]);
@@ -535,17 +600,16 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, status));
       tc_fence_after();
       if (ok) {
+        // result o: `width` columns starting at TMEM column col0; dS was stored without the scale; the
+        // single-sweep forward divides by the row sum here
+        auto store_out = [&](auto width, uint32_t col0, uint16_t* base, float mul) {
+          constexpr int DO = decltype(width)::value;
+          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * DO + half * (DO / 2);
 #pragma unroll
-        for (int o = 0; o < C::NOUT; ++o) {
-          uint16_t* dst = (o == 0 ? p.out0 : p.out1) +
-                          (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * D + half * (D / 2);
-          // dS was stored without the scale; the single-sweep forward divides by the row sum here
-          const float mul = MODE == FO_ONE ? inv_l : (o == 0 ? p.scale : 1.f);
-#pragma unroll
-          for (int ch = 0; ch < D / 32; ++ch) {
+          for (int ch = 0; ch < DO / 32; ++ch) {
             uint32_t v[16];
             if (n_iter > 0) {
-              tmem_ld16(tmem_base + lane_base + o * D + half * (D / 2) + 16 * ch, v);
+              tmem_ld16(tmem_base + lane_base + col0 + half * (DO / 2) + 16 * ch, v);
               tmem_wait_ld();
             } else {
 #pragma unroll
@@ -561,6 +625,40 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
               d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
+        };
+        // split operands: 64 fp32 columns, the sum of the two 64-column halves of the accumulator
+        auto store_out_split = [&](uint32_t col0, uint16_t* base16, float mul) {
+          float* dst = reinterpret_cast<float*>(base16) +
+                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * 64 + half * 32;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch) {
+            uint32_t a[16], b[16];
+            if (n_iter > 0) {
+              tmem_ld16(tmem_base + lane_base + col0 + half * 32 + 16 * ch, a);
+              tmem_ld16(tmem_base + lane_base + col0 + 64 + half * 32 + 16 * ch, b);
+              tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) a[j] = b[j] = 0u;
+            }
+            if (g_row < n_stat) {
+              float4* d4 = reinterpret_cast<float4*>(dst + 16 * ch);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                d4[j] = make_float4((__uint_as_float(a[4 * j]) + __uint_as_float(b[4 * j])) * mul,
+                                    (__uint_as_float(a[4 * j + 1]) + __uint_as_float(b[4 * j + 1])) * mul,
+                                    (__uint_as_float(a[4 * j + 2]) + __uint_as_float(b[4 * j + 2])) * mul,
+                                    (__uint_as_float(a[4 * j + 3]) + __uint_as_float(b[4 * j + 3])) * mul);
+            }
+          }
+        };
+        const float mul0 = MODE == FO_ONE ? inv_l : p.scale;
+        if constexpr (SPLIT) {
+          store_out_split(0, p.out0, mul0);
+          if (C::NOUT == 2) store_out_split(C::OUT0_COLS, p.out1, 1.f);
+        } else {
+          store_out(std::integral_constant<int, (C::OUT0_COLS ? C::OUT0_COLS : 64)>{}, 0, p.out0, mul0);
+          if constexpr (C::NOUT == 2) store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
         }
       }
     }
@@ -575,24 +673,34 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
   }
 }
 
-template <int MODE, int D, bool F16>
+template <int MODE, int DQK, int DV, bool F16, bool SPLIT = false>
 int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
-  using C = FoCfg<MODE, D>;
+  using C = FoCfg<MODE, DQK, DV>;
   const void* q_side[2] = {p.q, p.d_o};
   const void* k_side[2] = {p.k, p.v};
+  if (SPLIT) {
+    // the bf16 hi/lo copies the caller of this function left in the workspace
+    SplitBuffers sb = split_buffers(p);
+    q_side[0] = sb.q; q_side[1] = sb.d_o;
+    k_side[0] = sb.k; k_side[1] = sb.v;
+  }
   int st = FHOB_OK;
   if (MODE != FO_BK) {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, D, BM, F16);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, D, C::BN, F16);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
+      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
+      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, C::tile_d(i), C::BN, F16);
   } else {
-    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i) st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, D, BM, F16);
-    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i) st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, D, C::BN, F16);
+    for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
+      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BM, F16);
+    for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
+      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, C::tile_d(i), C::BN, F16);
   }
   if (st != FHOB_OK) return st;
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = MODE == FO_BK ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
-  constexpr auto kernel = fo_kernel<MODE, D, F16>;
+  constexpr auto kernel = fo_kernel<MODE, DQK, DV, F16, SPLIT>;
   {
     const int st_attr = allow_smem(kernel, C::SMEM_BYTES);
     if (st_attr != FHOB_OK) return st_attr;
@@ -617,18 +725,18 @@ int check_device() {
   return FHOB_OK;
 }
 
-template <int D, bool F16>
+template <int DQK, int DV, bool F16, bool SPLIT = false>
 int forward_impl(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   FoParams tp;
   memset(&tp, 0, sizeof(tp));
   tp.status = status;
   tp.lse_out = lse_out;
   tp.out0 = static_cast<uint16_t*>(o_out);
-  // no O wanted: the scores alone, reduced to the logsumexp
-  return o_out ? fo_launch<FO_ONE, D, F16>(p, tp, s) : fo_launch<FO_LSE, D, F16>(p, tp, s);
+  // no O wanted: the scores alone, reduced to the logsumexp (no tile of the second head dim is touched)
+  return o_out ? fo_launch<FO_ONE, DQK, DV, F16, SPLIT>(p, tp, s) : fo_launch<FO_LSE, DQK, DQK, F16, SPLIT>(p, tp, s);
 }
 
-template <int D, bool F16>
+template <int DQK, int DV, bool F16, bool SPLIT = false>
 int backward_impl(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s) {
   RowVectors rv = row_vectors(p);
   FoParams tp;
@@ -637,11 +745,11 @@ int backward_impl(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream
   tp.nlc = rv.nlc;
   tp.k1 = rv.k1;
   tp.out0 = static_cast<uint16_t*>(dq);
-  int st = fo_launch<FO_BQ, D, F16>(p, tp, s);
+  int st = fo_launch<FO_BQ, DQK, DV, F16, SPLIT>(p, tp, s);
   if (st != FHOB_OK) return st;
   tp.out0 = static_cast<uint16_t*>(dk);
   tp.out1 = static_cast<uint16_t*>(dv);
-  return fo_launch<FO_BK, D, F16>(p, tp, s);
+  return fo_launch<FO_BK, DQK, DV, F16, SPLIT>(p, tp, s);
 }
 
 // One warp waits on an mbarrier nothing ever arrives on: exercises the give-up branch of wait_bar.
@@ -668,29 +776,55 @@ int tc_selftest_expired_wait(int* status, cudaStream_t s) {
   return FHOB_OK;
 }
 
-// the first-order kernels take one head dim; problems with d_v != d run on the CUDA-core kernels
-bool tc_first_order_supported(const FhobProblem& p) {
-  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && tc_supported(p) && head_dim_v(p) == p.d;
+// 16-bit problems with head dims in {64, 128} (any combination), and fp32 problems with both head
+// dims 64 whose workspace holds the bf16 hi/lo copies (see tc_split_supported)
+bool tc_first_order_supported(const FhobProblem& p) { return tc_supported(p); }
+
+namespace {
+template <bool F16, class Fn>
+int by_dims(const FhobProblem& p, Fn&& fn) {
+  const int dv = head_dim_v(p);
+  if (p.d == 64) return dv == 64 ? fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 64>{})
+                                 : fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 128>{});
+  return dv == 64 ? fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 64>{})
+                  : fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 128>{});
 }
+}  // namespace
 
 int tc_forward(const FhobProblem& p, void* o_out, float* lse_out, int* status, cudaStream_t s) {
   if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;
   int st = check_device();
   if (st != FHOB_OK) return st;
+  if (p.dtype == FHOB_F32) {
+    st = tc_split_inputs(p, s, kSplitQ | kSplitK | (o_out ? kSplitV : 0));
+    if (st != FHOB_OK) return st;
+    return forward_impl<128, 128, false, true>(p, o_out, lse_out, status, s);
+  }
   if (p.dtype == FHOB_F16)
-    return p.d == 64 ? forward_impl<64, true>(p, o_out, lse_out, status, s)
-                     : forward_impl<128, true>(p, o_out, lse_out, status, s);
-  return p.d == 64 ? forward_impl<64, false>(p, o_out, lse_out, status, s)
-                   : forward_impl<128, false>(p, o_out, lse_out, status, s);
+    return by_dims<true>(p, [&](auto dqk, auto dv) {
+      return forward_impl<decltype(dqk)::value, decltype(dv)::value, true>(p, o_out, lse_out, status, s);
+    });
+  return by_dims<false>(p, [&](auto dqk, auto dv) {
+    return forward_impl<decltype(dqk)::value, decltype(dv)::value, false>(p, o_out, lse_out, status, s);
+  });
 }
 
 int tc_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStream_t s) {
   if (!tc_first_order_supported(p)) return FHOB_ERR_SHAPE;
   int st = check_device();
   if (st != FHOB_OK) return st;
+  if (p.dtype == FHOB_F32) {
+    st = tc_split_inputs(p, s, kSplitQ | kSplitK | kSplitV | kSplitDO);
+    if (st != FHOB_OK) return st;
+    return backward_impl<128, 128, false, true>(p, dq, dk, dv, s);
+  }
   if (p.dtype == FHOB_F16)
-    return p.d == 64 ? backward_impl<64, true>(p, dq, dk, dv, s) : backward_impl<128, true>(p, dq, dk, dv, s);
-  return p.d == 64 ? backward_impl<64, false>(p, dq, dk, dv, s) : backward_impl<128, false>(p, dq, dk, dv, s);
+    return by_dims<true>(p, [&](auto dqk, auto dvv) {
+      return backward_impl<decltype(dqk)::value, decltype(dvv)::value, true>(p, dq, dk, dv, s);
+    });
+  return by_dims<false>(p, [&](auto dqk, auto dvv) {
+    return backward_impl<decltype(dqk)::value, decltype(dvv)::value, false>(p, dq, dk, dv, s);
+  });
 }
 
 }  // namespace fhob

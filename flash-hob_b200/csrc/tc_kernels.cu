@@ -965,12 +965,14 @@ bool tc_split_supported(const FhobProblem& p) {
          p.workspace_bytes >= split_workspace_bytes(p);
 }
 
-int tc_split_inputs(const FhobProblem& p, cudaStream_t s) {
+int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which) {
   if (!tc_split_supported(p)) return FHOB_ERR_SHAPE;
   SplitBuffers sb = split_buffers(p);
-  const void* src[7] = {p.q, p.ddq, p.d_o, p.k, p.ddk, p.v, p.ddv};
+  const void* src[7] = {p.q, p.ddq, p.d_o, p.k, p.ddk, p.v, p.ddv};   // bit i of `which` = tensor i
   void* dst[7] = {sb.q, sb.ddq, sb.d_o, sb.k, sb.ddk, sb.v, sb.ddv};
   for (int i = 0; i < 7; ++i) {
+    if (!(which & (1 << i))) continue;
+    if (!src[i]) return FHOB_ERR_ARG;
     const long rows = static_cast<long>(p.bh) * (i < 3 ? p.n_q : p.n_k);
     const long pairs = rows * 32;
     split_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(

@@ -287,8 +287,10 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     ``L`` — the two tensors ``flash_bwdbwd`` consumes.  Role of the reference's
     forward kernel and ``produce_L`` (fhog/triton_flash.py:12-133, :252-258),
     which is dense, returns L in the input dtype and raises for causal masks.
-    16-bit inputs with D in {64, 128} run on the tensor cores (one sweep over
-    the keys with an online softmax), everything else on CUDA cores.
+    16-bit inputs with head dims in {64, 128} (V may have its own) and fp32
+    inputs with head dim 64 (split into bf16 hi + lo pairs) run on the tensor
+    cores (one sweep over the keys with an online softmax), everything else on
+    CUDA cores.
     ``need_o=False`` skips the ``P V`` product and returns ``(None, L)``.
     ``check`` synchronises and raises if a bounded device wait ran out.
     Queries that see no key (causal with N_K < N_Q) get ``O = 0``, ``L = -inf``.
@@ -316,7 +318,10 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     lib = _lib.load()
-    ws = _workspace(q.device, stream, 256)   # receives the status word
+    # receives the status word; fp32 with head dim 64: also the bf16 hi/lo copies of the inputs that
+    # let the problem run on the tensor cores
+    p.n_k = k.shape[1]
+    ws = _workspace(q.device, stream, max(256, lib.fhob_workspace_bytes_problem(C.byref(p))))
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
     with torch.cuda.device(q.device):
         _lib.check(lib.fhob_forward(C.byref(p), C.c_void_p(o.data_ptr() if need_o else None),

@@ -215,8 +215,10 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
  * window, impl; writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).
  * `o_out` may be NULL when only the logsumexp is wanted (the role of
  * produce_L): the P V product is then skipped altogether.
- * 16-bit inputs with d = d_v in {64, 128} run on the tensor cores (impl AUTO
- * or TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
+ * 16-bit inputs with head dims in {64, 128} (d_v may differ from d) and fp32
+ * inputs with both head dims 64 and a workspace of
+ * fhob_workspace_bytes_problem() bytes (split bf16 operands) run on the tensor
+ * cores (impl AUTO or TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
  * that ran out) go to the status word at the start of p->workspace, or, when
  * p->workspace is NULL, to a word the library keeps per device; either is
  * cleared by the call and read with fhob_read_status(p, stream).

@@ -113,6 +113,18 @@ def test_fp32_tensor_core_path(bh, nq, nk, causal, window):
             assert res["status"] == 0
             for n, r in zip(("d", "dd", "b"), stats):
                 assert O.rel_err(res[n], r) < TOL_F32, (n, fused)
+    # the producers either side, same scheme: forward (O and L), logsumexp alone, first backward
+    live = slice(nq - nk if (causal and nk < nq) else 0, None)
+    o_dev, lse_dev = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, check=True, **kw)
+    assert o_dev.dtype == torch.float32
+    assert O.rel_err(o_dev[:, live], o[:, live]) < TOL_F32 and O.rel_err(lse_dev[:, live], lse[:, live]) < 1e-5
+    _, lse_only = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, need_o=False, **kw)
+    assert O.rel_err(lse_only[:, live], lse[:, live]) < 1e-5
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], args[3], dev["do"], args[8], scale, **kw)
+    xl = {n: (t[:, live] if n in ("q", "do") else t) for n, t in x.items()}
+    first_ref = O.attn_bwd(xl["q"], xl["k"], xl["v"], xl["do"], scale, causal, sliding_window_length=wl)
+    assert O.rel_err(first[0][:, live], first_ref[0]) < TOL_F32
+    assert O.rel_err(first[1], first_ref[1]) < TOL_F32 and O.rel_err(first[2], first_ref[2]) < TOL_F32
 
 
 def test_fp32_tensor_core_path_needs_head_dim_64_and_a_larger_workspace():
@@ -838,8 +850,8 @@ def test_value_head_dim_differs_from_query_key_head_dim(bh, nq, nk, dqk, dv, cau
         got = fhob.flash_bwdbwd(*args[:3], None, *args[4:], check=True, **kw)     # D from the sweep
         for n, g, r in zip(OUT_NAMES, got, ref):
             assert O.rel_err(g, r) < tol, n
-    # the producers either side (CUDA cores when the two dims differ)
-    fkw = dict(kw, impl="auto")
+    # the producers either side: same kernel family as the operator
+    fkw = dict(kw)
     o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **fkw)
     assert o.shape == (bh, nq, dv) and O.rel_err(o, o_ref) < tol and O.rel_err(lse, l_ref) < 1e-5
     first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **fkw)
