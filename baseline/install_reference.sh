@@ -1,13 +1,15 @@
 #!/bin/bash
 # Installs the unmodified reference package (fhog) into baseline/_ref, offline.
 #
+#     baseline/install_reference.sh <path of the reference checkout>
+#
 # The reference declares the `uv_build` build backend, which is not available without a network,
-# so `pip install /root/reference` stops with "No module named 'uv_build'".  This recipe installs
+# so a plain `pip install <checkout>` stops with "No module named 'uv_build'".  This recipe installs
 # from a scratch copy whose only change is the [build-system] table of pyproject.toml (setuptools
 # instead of uv_build, same package list); every installed .py file is byte-identical to the
 # reference's.  baseline/_ref is git-ignored: it is a build product, not source of this repo.
 set -euo pipefail
-SRC=${1:-/root/reference}
+SRC=${1:?usage: install_reference.sh <path of the reference checkout>}
 HERE=$(cd "$(dirname "$0")" && pwd)
 TMP=$(mktemp -d /tmp/fhog_ref_XXXXXX)
 cp -r "$SRC"/. "$TMP"/
