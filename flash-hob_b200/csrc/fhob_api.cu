@@ -158,7 +158,7 @@ const char* fhob_strerror(int status) {
     case FHOB_OK: return "ok";
     case FHOB_ERR_ARG: return "invalid argument (null pointer, bad dtype/impl/causal flag or non-positive size)";
     case FHOB_ERR_SHAPE: return "shape not supported (head dims must keep rows 16-byte aligned and be <= 128; "
-                                "the tensor-core kernels need 16-bit elements and head dims in {64,128})";
+                                "the tensor-core kernels need 16-bit elements, or fp32 with both head dims 64)";
     case FHOB_ERR_ALIGN: return "a tensor pointer is not 16-byte aligned";
     case FHOB_ERR_WORKSPACE: return "workspace missing, misaligned (256 B) or smaller than fhob_workspace_bytes() "
                                     "(fp32 on the tensor cores: smaller than fhob_workspace_bytes_problem())";

@@ -73,6 +73,7 @@ struct FoParams {
   uint16_t* out1;     // BK: dV
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
+  int d_out0, d_out1;   // columns of the results in memory (<= the tile widths; see fo_launch)
   float scale;
 };
 
@@ -602,9 +603,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
       if (ok) {
         // result o: `width` columns starting at TMEM column col0; dS was stored without the scale; the
         // single-sweep forward divides by the row sum here
-        auto store_out = [&](auto width, uint32_t col0, uint16_t* base, float mul) {
-          constexpr int DO = decltype(width)::value;
-          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * DO + half * (DO / 2);
+        auto store_out = [&](auto width, int d_mem, uint32_t col0, uint16_t* base, float mul) {
+          constexpr int DO = decltype(width)::value;   // columns of the accumulator; d_mem <= DO of them exist in memory
+          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * d_mem + half * (DO / 2);
 #pragma unroll
           for (int ch = 0; ch < DO / 32; ++ch) {
             uint32_t v[16];
@@ -621,8 +622,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
               for (int j = 0; j < 8; ++j)
                 w[j] = pack16<F16>(__uint_as_float(v[2 * j]) * mul, __uint_as_float(v[2 * j + 1]) * mul);
               uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
-              d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              const int c0 = half * (DO / 2) + 16 * ch;   // head dims are multiples of 8: 16-byte pieces are whole
+              if (c0 + 8 <= d_mem) d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              if (c0 + 16 <= d_mem) d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
         };
@@ -657,8 +659,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           store_out_split(0, p.out0, mul0);
           if (C::NOUT == 2) store_out_split(C::OUT0_COLS, p.out1, 1.f);
         } else {
-          store_out(std::integral_constant<int, (C::OUT0_COLS ? C::OUT0_COLS : 64)>{}, 0, p.out0, mul0);
-          if constexpr (C::NOUT == 2) store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
+          store_out(std::integral_constant<int, (C::OUT0_COLS ? C::OUT0_COLS : 64)>{}, p.d_out0, 0, p.out0, mul0);
+          if constexpr (C::NOUT == 2) store_out(std::integral_constant<int, DV>{}, p.d_out1, C::OUT0_COLS, p.out1, 1.f);
         }
       }
     }
@@ -684,19 +686,23 @@ int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
     q_side[0] = sb.q; q_side[1] = sb.d_o;
     k_side[0] = sb.k; k_side[1] = sb.v;
   }
+  // head dims below the tile widths: the boxes reach past the end of a row and are zero-filled there
+  const int d_mem[2] = {SPLIT ? 128 : p.d, SPLIT ? 128 : head_dim_v(p)};
   int st = FHOB_OK;
   if (MODE != FO_BK) {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BM, F16);
+      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, d_mem[i], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, C::tile_d(i), C::BN, F16);
+      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, d_mem[i], C::BN, F16);
   } else {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BM, F16);
+      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, d_mem[i], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, C::tile_d(i), C::BN, F16);
+      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i], C::BN, F16);
   }
   if (st != FHOB_OK) return st;
+  tp.d_out0 = MODE == FO_ONE ? d_mem[1] : d_mem[0];   // O | dQ | dK
+  tp.d_out1 = d_mem[1];                               // dV
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = MODE == FO_BK ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;
@@ -784,9 +790,10 @@ namespace {
 template <bool F16, class Fn>
 int by_dims(const FhobProblem& p, Fn&& fn) {
   const int dv = head_dim_v(p);
-  if (p.d == 64) return dv == 64 ? fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 64>{})
+  // tile widths: the head dims rounded up to 64 or 128
+  if (p.d <= 64) return dv <= 64 ? fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 64>{})
                                  : fn(std::integral_constant<int, 64>{}, std::integral_constant<int, 128>{});
-  return dv == 64 ? fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 64>{})
+  return dv <= 64 ? fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 64>{})
                   : fn(std::integral_constant<int, 128>{}, std::integral_constant<int, 128>{});
 }
 }  // namespace

@@ -108,6 +108,7 @@ struct TcParams {
   uint16_t* out1;
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
+  int d_out0, d_out1;   // columns of the two results in memory (<= the tile widths DQK, DV; see launch)
   float scale;
 };
 
@@ -783,9 +784,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
       if (n_iter > 0) ok = ok && __all_sync(0xffffffffu, wait_bar(&bars->out_full, 0, bars, p.status));
       tc_fence_after();
       if (ok) {
-        auto store_out = [&](auto width, uint32_t col0, uint16_t* base, float mul) {
-          constexpr int DO = decltype(width)::value;   // columns of this result
-          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * DO + half * (DO / 2);
+        auto store_out = [&](auto width, int d_mem, uint32_t col0, uint16_t* base, float mul) {
+          constexpr int DO = decltype(width)::value;   // columns of the accumulator; d_mem <= DO of them exist in memory
+          uint16_t* dst = base + (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * d_mem + half * (DO / 2);
 #pragma unroll
           for (int ch = 0; ch < DO / 32; ++ch) {
             uint32_t v[16];
@@ -802,8 +803,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
               for (int j = 0; j < 8; ++j)
                 w[j] = pack16<F16>(__uint_as_float(v[2 * j]) * mul, __uint_as_float(v[2 * j + 1]) * mul);
               uint4* d4 = reinterpret_cast<uint4*>(dst + 16 * ch);
-              d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
-              d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
+              const int c0 = half * (DO / 2) + 16 * ch;   // head dims are multiples of 8: 16-byte pieces are whole
+              if (c0 + 8 <= d_mem) d4[0] = make_uint4(w[0], w[1], w[2], w[3]);
+              if (c0 + 16 <= d_mem) d4[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
           }
         };
@@ -838,8 +840,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           store_out_split(0, p.out0, c.scale);
           store_out_split(C::OUT0_COLS, p.out1, 1.f);
         } else {
-          store_out(std::integral_constant<int, DQK>{}, 0, p.out0, c.scale);
-          store_out(std::integral_constant<int, DV>{}, C::OUT0_COLS, p.out1, 1.f);
+          store_out(std::integral_constant<int, DQK>{}, p.d_out0, 0, p.out0, c.scale);
+          store_out(std::integral_constant<int, DV>{}, p.d_out1, C::OUT0_COLS, p.out1, 1.f);
         }
       }
     }
@@ -884,19 +886,25 @@ int launch(const FhobProblem& p, cudaStream_t s) {
     q_side[0] = sb.q; q_side[1] = sb.ddq; q_side[2] = sb.d_o;
     k_side[0] = sb.k; k_side[1] = sb.ddk; k_side[2] = sb.v; k_side[3] = sb.ddv;
   }
+  // A head dim below the tile width (any multiple of 8 up to 128) needs nothing but the right
+  // tensor map: the 64-column boxes reach past the end of a row, the TMA unit fills those columns
+  // with zeros, zeros add nothing to a contraction, and the epilogue stores only the columns that exist.
+  const int d_mem[2] = {SPLIT ? 128 : p.d, SPLIT ? 128 : head_dim_v(p)};   // columns in memory of the two tile kinds
   int st = FHOB_OK;
   if (PASS != 4) {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BM, F16);
+      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, d_mem[i < 2 ? 0 : 1], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BN, F16);
+      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, d_mem[i < 2 ? 0 : 1], BN, F16);
   } else {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, C::tile_d(i), BM, F16);
+      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, d_mem[i < 2 ? 0 : 1], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, C::tile_d(i), BN, F16);
+      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i < 2 ? 0 : 1], BN, F16);
   }
   if (st != FHOB_OK) return st;
+  tp.d_out0 = d_mem[0];
+  tp.d_out1 = d_mem[1];
   tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
   tp.out0 = static_cast<uint16_t*>(PASS == 3 ? p.dq2 : p.dk2);
   tp.out1 = static_cast<uint16_t*>(PASS == 3 ? p.ddo : p.dv2);
@@ -932,9 +940,10 @@ int dispatch(int pass, const FhobProblem& p, cudaStream_t s) {
 
 template <bool F16>
 int dispatch_dims(int pass, const FhobProblem& p, cudaStream_t s) {
+  // tile widths: the head dims rounded up to 64 or 128
   const int dv = head_dim_v(p);
-  if (p.d == 64) return dv == 64 ? dispatch<64, 64, F16>(pass, p, s) : dispatch<64, 128, F16>(pass, p, s);
-  return dv == 64 ? dispatch<128, 64, F16>(pass, p, s) : dispatch<128, 128, F16>(pass, p, s);
+  if (p.d <= 64) return dv <= 64 ? dispatch<64, 64, F16>(pass, p, s) : dispatch<64, 128, F16>(pass, p, s);
+  return dv <= 64 ? dispatch<128, 64, F16>(pass, p, s) : dispatch<128, 128, F16>(pass, p, s);
 }
 
 int check_arch() {
@@ -955,7 +964,9 @@ int check_arch() {
 bool tc_supported(const FhobProblem& p) {
   const int dv = head_dim_v(p);
   if (p.dtype == FHOB_F32) return tc_split_supported(p);
-  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && (p.d == 64 || p.d == 128) && (dv == 64 || dv == 128);
+  // 16-bit storage: any head dims up to 128 whose rows stay 16-byte aligned
+  return (p.dtype == FHOB_BF16 || p.dtype == FHOB_F16) && p.d > 0 && p.d <= 128 && p.d % 8 == 0 && dv <= 128 &&
+         dv % 8 == 0;
 }
 
 // fp32 problems take the tensor-core path when both head dims are 64 and the workspace has room

@@ -170,7 +170,7 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     and ``ddV`` may have a head dim of their own (the reference operator has a
     single D, :577; its maths does not need that, jax_refs/flash_impl.py:381-389):
     ``dV2`` and ``ddO`` then have it too; the tensor-core kernels take head dims
-    64 and 128 in any combination.  ``L`` is the logsumexp of
+    any head dims up to 128 that are multiples of 8.  ``L`` is the logsumexp of
     the masked scaled scores, any float dtype (used as fp32).  ``O`` may be
     ``None`` for 16-bit inputs on the tensor-core path: ``D = rowsum(dO * O)``
     (reference :580) is then replaced by the mathematically equal
@@ -287,7 +287,7 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     ``L`` — the two tensors ``flash_bwdbwd`` consumes.  Role of the reference's
     forward kernel and ``produce_L`` (fhog/triton_flash.py:12-133, :252-258),
     which is dense, returns L in the input dtype and raises for causal masks.
-    16-bit inputs with head dims in {64, 128} (V may have its own) and fp32
+    16-bit inputs with head dims up to 128, multiples of 8 (V may have its own), and fp32
     inputs with head dim 64 (split into bf16 hi + lo pairs) run on the tensor
     cores (one sweep over the keys with an online softmax), everything else on
     CUDA cores.

@@ -31,7 +31,7 @@ extern "C" {
 enum { FHOB_BF16 = 0, FHOB_F32 = 1, FHOB_F16 = 2 };
 
 /* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for 16-bit
- * elements (head dims 64 or 128) and for fp32 with both head dims 64 when the
+ * elements (head dims up to 128, multiples of 8) and for fp32 with both head dims 64 when the
  * workspace has fhob_workspace_bytes_problem() bytes; CUDA-core kernels for
  * everything else.  SIMT forces the CUDA-core kernels for any type
  * (debugging aid; same four passes, same row statistics). */
@@ -215,7 +215,7 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
  * window, impl; writes `o_out` (bh, n_q, d) and `lse_out` (bh, n_q).
  * `o_out` may be NULL when only the logsumexp is wanted (the role of
  * produce_L): the P V product is then skipped altogether.
- * 16-bit inputs with head dims in {64, 128} (d_v may differ from d) and fp32
+ * 16-bit inputs with head dims up to 128 (multiples of 8; d_v may differ from d) and fp32
  * inputs with both head dims 64 and a workspace of
  * fhob_workspace_bytes_problem() bytes (split bf16 operands) run on the tensor
  * cores (impl AUTO or TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait

@@ -64,7 +64,7 @@ def _problem(**over):
     (dict(impl=9), 1), (dict(causal=2), 1),
     (dict(window=16), 1), (dict(causal=1, window=-1), 1), (dict(d_v=-8), 1),
     (dict(d=129), 2), (dict(d=4), 2), (dict(d=256), 2), (dict(d_v=4), 2), (dict(d_v=136), 2),
-    (dict(impl=2, dtype=1, d=128), 2), (dict(impl=2, d=32), 2), (dict(impl=2, d_v=96), 2),
+    (dict(impl=2, dtype=1, d=128), 2), (dict(impl=2, d=36), 2), (dict(impl=2, d_v=100), 2),
     (dict(impl=2, dtype=1, workspace_bytes=20000), 4),   # fp32 on the tensor cores needs room for the hi/lo copies
     (dict(k=0x10008), 3), (dict(ddo=0x20004), 3),
     (dict(workspace=None), 4), (dict(workspace_bytes=100), 4), (dict(workspace=0x100010), 4),

@@ -391,9 +391,9 @@ def test_wrong_inputs_raise():
     with pytest.raises(TypeError):
         qd = q.double()
         fhob.flash_bwdbwd(qd, qd, qd, qd, qd, qd, qd, qd, L, 0.125)
-    q32 = torch.zeros(2, 128, 32, device="cuda", dtype=torch.bfloat16)
+    q36 = torch.zeros(2, 128, 36, device="cuda", dtype=torch.bfloat16)    # rows of 72 bytes: not 16-byte aligned
     with pytest.raises(RuntimeError, match="shape not supported"):
-        fhob.flash_bwdbwd(q32, q32, q32, q32, q32, q32, q32, q32, L, 0.125, impl="tcgen05")
+        fhob.flash_bwdbwd(q36, q36, q36, q36, q36, q36, q36, q36, L, 0.125, impl="tcgen05")
 
 
 @pytest.mark.parametrize("causal", [False, True])
@@ -879,6 +879,35 @@ def test_two_head_dims_through_autograd_and_host_buffers():
     got = fhob.flash_bwdbwd(*host, lse, scale, is_causal=True)
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert g.device.type == "cpu" and g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,nq,nk,dqk,dv", [(2, 256, 384, 32, 32), (2, 200, 328, 96, 96), (1, 384, 384, 80, 40),
+                                             (2, 130, 259, 8, 120), (1, 256, 256, 104, 128), (2, 192, 320, 64, 48)])
+def test_head_dims_that_are_not_64_or_128_on_the_tensor_cores(bh, nq, nk, dqk, dv, causal):
+    """Any head dims up to 128 that keep rows 16-byte aligned (multiples of 8) run on the tensor-core
+    kernels: the TMA boxes reach past the end of a row and are zero-filled there.  Operator (with
+    and without the saved output), forward and first backward against the oracle."""
+    import fhob
+    x = _two_dim_inputs(bh, nq, nk, dqk, dv, seed=431)
+    scale = dqk ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal)
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal)
+    dev = {k: v.bfloat16().cuda() for k, v in x.items()}
+    kw = dict(is_causal=causal, impl="tcgen05")
+    args = (dev["q"], dev["k"], dev["v"], o_ref.bfloat16().cuda(), dev["do"], dev["ddq"], dev["ddk"], dev["ddv"],
+            l_ref.float().cuda(), scale)
+    for a in (args, args[:3] + (None,) + args[4:]):
+        got = fhob.flash_bwdbwd(*a, check=True, **kw)
+        for n, g, r in zip(OUT_NAMES, got, ref):
+            assert g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, check=True, **kw)
+    assert o.shape == (bh, nq, dv) and O.rel_err(o, o_ref) < TOL_BF16 and O.rel_err(lse, l_ref) < 1e-5
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **kw)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, causal)
+    for n, g, r in zip(("dq", "dk", "dv"), first, first_ref):
+        assert g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
 
 
 def test_preallocated_outputs_and_workspace():
