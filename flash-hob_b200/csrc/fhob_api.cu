@@ -125,7 +125,7 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->workspace_bytes < fhob_workspace_bytes(p->bh, p->n_q)) return FHOB_ERR_WORKSPACE;
   if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) {
     // fp32 with both head dims 64 runs on the tensor cores if the workspace also holds the bf16 hi/lo copies
-    if (p->dtype == FHOB_F32 && p->d == 64 && dv == 64) return FHOB_ERR_WORKSPACE;
+    if (split_dims_ok(*p)) return FHOB_ERR_WORKSPACE;
     return FHOB_ERR_SHAPE;
   }
   return FHOB_OK;
@@ -178,8 +178,7 @@ const char* fhob_last_cuda_error(void) { return g_cuda_error; }
 
 size_t fhob_workspace_bytes_problem(const FhobProblem* p) {
   if (!p || p->bh <= 0 || p->n_q <= 0 || p->n_k <= 0) return 0;
-  if (p->dtype == FHOB_F32 && p->impl != FHOB_IMPL_SIMT && p->d == 64 && head_dim_v(*p) == 64)
-    return split_workspace_bytes(*p);
+  if (p->impl != FHOB_IMPL_SIMT && split_dims_ok(*p)) return split_workspace_bytes(*p);
   return fhob_workspace_bytes(p->bh, p->n_q);
 }
 

@@ -65,6 +65,11 @@ struct SplitBuffers {
   void *q, *ddq, *d_o, *k, *ddk, *v, *ddv;
 };
 inline size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+// head dims the split scheme takes: rows of up to 64 fp32 columns, 16-byte aligned
+inline bool split_dims_ok(const FhobProblem& p) {
+  const int dv = head_dim_v(p);
+  return p.dtype == FHOB_F32 && p.d > 0 && p.d <= 64 && p.d % 4 == 0 && dv <= 64 && dv % 4 == 0;
+}
 inline size_t split_workspace_bytes(const FhobProblem& p) {
   const size_t q_bytes = align256(static_cast<size_t>(p.bh) * p.n_q * 256);
   const size_t k_bytes = align256(static_cast<size_t>(p.bh) * p.n_k * 256);

@@ -629,9 +629,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
           }
         };
         // split operands: 64 fp32 columns, the sum of the two 64-column halves of the accumulator
-        auto store_out_split = [&](uint32_t col0, uint16_t* base16, float mul) {
+        auto store_out_split = [&](int d_mem, uint32_t col0, uint16_t* base16, float mul) {
           float* dst = reinterpret_cast<float*>(base16) +
-                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * 64 + half * 32;
+                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * d_mem + half * 32;
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
             uint32_t a[16], b[16];
@@ -647,6 +647,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
               float4* d4 = reinterpret_cast<float4*>(dst + 16 * ch);
 #pragma unroll
               for (int j = 0; j < 4; ++j)
+                if (half * 32 + 16 * ch + 4 * j + 4 <= d_mem)   // head dims are multiples of 4: float4 pieces are whole
                 d4[j] = make_float4((__uint_as_float(a[4 * j]) + __uint_as_float(b[4 * j])) * mul,
                                     (__uint_as_float(a[4 * j + 1]) + __uint_as_float(b[4 * j + 1])) * mul,
                                     (__uint_as_float(a[4 * j + 2]) + __uint_as_float(b[4 * j + 2])) * mul,
@@ -656,8 +657,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
         };
         const float mul0 = MODE == FO_ONE ? inv_l : p.scale;
         if constexpr (SPLIT) {
-          store_out_split(0, p.out0, mul0);
-          if (C::NOUT == 2) store_out_split(C::OUT0_COLS, p.out1, 1.f);
+          store_out_split(p.d_out0, 0, p.out0, mul0);
+          if (C::NOUT == 2) store_out_split(p.d_out1, C::OUT0_COLS, p.out1, 1.f);
         } else {
           store_out(std::integral_constant<int, (C::OUT0_COLS ? C::OUT0_COLS : 64)>{}, p.d_out0, 0, p.out0, mul0);
           if constexpr (C::NOUT == 2) store_out(std::integral_constant<int, DV>{}, p.d_out1, C::OUT0_COLS, p.out1, 1.f);
@@ -701,8 +702,8 @@ int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
       st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i], C::BN, F16);
   }
   if (st != FHOB_OK) return st;
-  tp.d_out0 = MODE == FO_ONE ? d_mem[1] : d_mem[0];   // O | dQ | dK
-  tp.d_out1 = d_mem[1];                               // dV
+  tp.d_out0 = MODE == FO_ONE ? head_dim_v(p) : p.d;   // columns in memory of O | dQ | dK
+  tp.d_out1 = head_dim_v(p);                          // dV
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;
   const int n_stat = MODE == FO_BK ? p.n_k : p.n_q;
   tp.tiles_per_head = (n_stat + BM - 1) / BM;

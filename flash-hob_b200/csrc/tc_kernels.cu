@@ -810,9 +810,9 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
           }
         };
         // split operands: a result has 64 fp32 columns, the sum of the two 64-column halves of its accumulator
-        auto store_out_split = [&](uint32_t col0, uint16_t* base16, float mul) {
+        auto store_out_split = [&](int d_mem, uint32_t col0, uint16_t* base16, float mul) {
           float* dst = reinterpret_cast<float*>(base16) +
-                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * 64 + half * 32;
+                       (static_cast<size_t>(head) * n_stat + (g_row < n_stat ? g_row : 0)) * d_mem + half * 32;
 #pragma unroll
           for (int ch = 0; ch < 2; ++ch) {
             uint32_t a[16], b[16];
@@ -828,6 +828,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
               float4* d4 = reinterpret_cast<float4*>(dst + 16 * ch);
 #pragma unroll
               for (int j = 0; j < 4; ++j)
+                if (half * 32 + 16 * ch + 4 * j + 4 <= d_mem)   // head dims are multiples of 4: float4 pieces are whole
                 d4[j] = make_float4((__uint_as_float(a[4 * j]) + __uint_as_float(b[4 * j])) * mul,
                                     (__uint_as_float(a[4 * j + 1]) + __uint_as_float(b[4 * j + 1])) * mul,
                                     (__uint_as_float(a[4 * j + 2]) + __uint_as_float(b[4 * j + 2])) * mul,
@@ -837,8 +838,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
         };
         // dS and dS2 were stored without the factor `scale`: it is applied to dQ2 | dK2 here
         if constexpr (SPLIT) {
-          store_out_split(0, p.out0, c.scale);
-          store_out_split(C::OUT0_COLS, p.out1, 1.f);
+          store_out_split(p.d_out0, 0, p.out0, c.scale);
+          store_out_split(p.d_out1, C::OUT0_COLS, p.out1, 1.f);
         } else {
           store_out(std::integral_constant<int, DQK>{}, p.d_out0, 0, p.out0, c.scale);
           store_out(std::integral_constant<int, DV>{}, p.d_out1, C::OUT0_COLS, p.out1, 1.f);
@@ -858,13 +859,14 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
 // ------------------------------------------------------------------ host side
 
-// fp32 -> [hi(64) | lo(64)] bf16 rows (see split_pack): one thread per pair of columns.
-__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs) {
+// fp32 rows of d <= 64 columns -> [hi(64) | lo(64)] bf16 rows (see split_pack), zero beyond d: one
+// thread per pair of columns of the 64-wide row.
+__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs, int d) {
   const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= pairs) return;
   const long row = i >> 5;          // 32 pairs of columns per row of 64
   const int c2 = static_cast<int>(i & 31);
-  const float2 x = reinterpret_cast<const float2*>(src)[i];
+  const float2 x = 2 * c2 < d ? *reinterpret_cast<const float2*>(src + row * d + 2 * c2) : make_float2(0.f, 0.f);
   uint32_t hi, lo;
   split_pack(x.x, x.y, hi, lo);
   dst[row * 64 + c2] = hi;          // a split row is 128 bf16 = 64 words: hi in words [0, 32), lo in [32, 64)
@@ -903,8 +905,8 @@ int launch(const FhobProblem& p, cudaStream_t s) {
       st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i < 2 ? 0 : 1], BN, F16);
   }
   if (st != FHOB_OK) return st;
-  tp.d_out0 = d_mem[0];
-  tp.d_out1 = d_mem[1];
+  tp.d_out0 = p.d;               // columns of the results in memory (split operands: up to 64 fp32 columns)
+  tp.d_out1 = head_dim_v(p);
   tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
   tp.out0 = static_cast<uint16_t*>(PASS == 3 ? p.dq2 : p.dk2);
   tp.out1 = static_cast<uint16_t*>(PASS == 3 ? p.ddo : p.dv2);
@@ -969,11 +971,11 @@ bool tc_supported(const FhobProblem& p) {
          dv % 8 == 0;
 }
 
-// fp32 problems take the tensor-core path when both head dims are 64 and the workspace has room
-// for the bf16 hi/lo copies of the seven inputs (fhob_workspace_bytes_problem says how much)
+// fp32 problems take the tensor-core path when both head dims are at most 64 (and keep rows 16-byte
+// aligned) and the workspace has room for the bf16 hi/lo copies of the seven inputs
+// (fhob_workspace_bytes_problem says how much)
 bool tc_split_supported(const FhobProblem& p) {
-  return p.dtype == FHOB_F32 && p.d == 64 && head_dim_v(p) == 64 && p.workspace &&
-         p.workspace_bytes >= split_workspace_bytes(p);
+  return split_dims_ok(p) && p.workspace && p.workspace_bytes >= split_workspace_bytes(p);
 }
 
 int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which) {
@@ -986,8 +988,9 @@ int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which) {
     if (!src[i]) return FHOB_ERR_ARG;
     const long rows = static_cast<long>(p.bh) * (i < 3 ? p.n_q : p.n_k);
     const long pairs = rows * 32;
+    const bool v_side = i == 2 || i >= 5;   // dO, V, ddV
     split_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(
-        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs);
+        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs, v_side ? head_dim_v(p) : p.d);
     FHOB_CUDA_OK(cudaGetLastError());
   }
   return FHOB_OK;

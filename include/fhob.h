@@ -31,7 +31,7 @@ extern "C" {
 enum { FHOB_BF16 = 0, FHOB_F32 = 1, FHOB_F16 = 2 };
 
 /* Kernel families.  AUTO = tcgen05/TMEM/TMA tensor-core kernels for 16-bit
- * elements (head dims up to 128, multiples of 8) and for fp32 with both head dims 64 when the
+ * elements (head dims up to 128, multiples of 8) and for fp32 with both head dims at most 64 when the
  * workspace has fhob_workspace_bytes_problem() bytes; CUDA-core kernels for
  * everything else.  SIMT forces the CUDA-core kernels for any type
  * (debugging aid; same four passes, same row statistics). */
@@ -120,7 +120,7 @@ size_t fhob_workspace_bytes(int32_t bh, int32_t n_q);
  * Bytes of scratch that let the library take its fastest path for this
  * particular problem (reads bh, n_q, n_k, d, d_v, dtype, impl).  Equal to
  * fhob_workspace_bytes(bh, n_q) except for fp32 problems with both head dims
- * 64: those run on the tensor cores (every fp32 operand as a bf16 hi + lo
+ * at most 64 (multiples of 4): those run on the tensor cores (every fp32 operand as a bf16 hi + lo
  * pair, three products per contraction, fp32 accumulation) if the workspace
  * also has room for the bf16 copies of the seven inputs (their size again:
  * still linear in the sequence lengths).  With a smaller workspace such a
@@ -216,7 +216,7 @@ int fhob_selftest_expired_wait(void* workspace, size_t workspace_bytes, void* st
  * `o_out` may be NULL when only the logsumexp is wanted (the role of
  * produce_L): the P V product is then skipped altogether.
  * 16-bit inputs with head dims up to 128 (multiples of 8; d_v may differ from d) and fp32
- * inputs with both head dims 64 and a workspace of
+ * inputs with both head dims at most 64 and a workspace of
  * fhob_workspace_bytes_problem() bytes (split bf16 operands) run on the tensor
  * cores (impl AUTO or TCGEN05), everything else on CUDA cores.  Device-side conditions (a wait
  * that ran out) go to the status word at the start of p->workspace, or, when

@@ -127,6 +127,34 @@ def test_fp32_tensor_core_path(bh, nq, nk, causal, window):
     assert O.rel_err(first[1], first_ref[1]) < TOL_F32 and O.rel_err(first[2], first_ref[2]) < TOL_F32
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("bh,nq,nk,dqk,dv", [(2, 256, 384, 32, 32), (2, 200, 328, 48, 64), (1, 320, 320, 64, 16),
+                                             (2, 130, 259, 4, 60)])
+def test_fp32_tensor_core_path_with_smaller_head_dims(bh, nq, nk, dqk, dv, causal):
+    """fp32 with head dims below 64 (multiples of 4): the bf16 hi/lo copies are padded to 64 columns."""
+    import fhob
+    g = torch.Generator().manual_seed(433)
+    shapes = dict(q=(bh, nq, dqk), k=(bh, nk, dqk), v=(bh, nk, dv), do=(bh, nq, dv),
+                  ddq=(bh, nq, dqk), ddk=(bh, nk, dqk), ddv=(bh, nk, dv))
+    x = {n: torch.randn(s, generator=g).bfloat16().double() for n, s in shapes.items()}
+    scale = dqk ** -0.5
+    ref = O.bwdbwd_closed_form(*x.values(), scale, causal)
+    o_ref = O.attn_fwd(x["q"], x["k"], x["v"], scale, causal)
+    l_ref = O.attn_lse(x["q"], x["k"], scale, causal)
+    dev = {k: v.float().cuda() for k, v in x.items()}
+    kw = dict(is_causal=causal, impl="tcgen05")
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o_ref.float().cuda(), dev["do"], dev["ddq"], dev["ddk"],
+                            dev["ddv"], l_ref.float().cuda(), scale, check=True, **kw)
+    for n, g_, r in zip(OUT_NAMES, got, ref):
+        assert g_.shape == r.shape and O.rel_err(g_, r) < TOL_F32, n
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, check=True, **kw)
+    assert o.shape == (bh, nq, dv) and O.rel_err(o, o_ref) < TOL_F32 and O.rel_err(lse, l_ref) < 1e-5
+    first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **kw)
+    first_ref = O.attn_bwd(x["q"], x["k"], x["v"], x["do"], scale, causal)
+    for n, g_, r in zip(("dq", "dk", "dv"), first, first_ref):
+        assert g_.shape == r.shape and O.rel_err(g_, r) < TOL_F32, n
+
+
 def test_fp32_tensor_core_path_needs_head_dim_64_and_a_larger_workspace():
     import fhob
     from fhob import _lib
