@@ -27,13 +27,17 @@ namespace {
 template <typename T>
 __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
                                float* __restrict__ nlc, float* __restrict__ k1, int* status, long rows, int d,
-                               int n_q, int first_live_query) {
+                               int n_q, int first_live_query, View vo, View vdo, long long lse_head,
+                               long long lse_batch) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
   long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   int lane = threadIdx.x & 31;
-  // the inputs are dense (bh*n_q rows), the row vectors are padded per head
-  const long vrow = (row / n_q) * row_stride(n_q) + row % n_q;
+  // the inputs may be views (strides per row / head / batch entry), the row vectors are padded per head
+  const long bh = row / n_q, qi = row - bh * n_q;
+  const long vrow = bh * row_stride(n_q) + qi;
+  const long hb = bh / vo.heads, hh = bh - hb * vo.heads;
+  const float lse_row = lse[hb * lse_batch + hh * lse_head + qi];
   if (row % n_q < first_live_query) {
     // a query the causal mask leaves without any visible key (n_k < n_q): every P of its row is
     // masked to zero in the passes, so the row contributes nothing and its dQ2 and ddO are zero.
@@ -46,18 +50,18 @@ __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_
   }
   if (o == nullptr) {
     // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
-    if (lane == 0) nlc[vrow] = -lse[row] * kLog2e;
+    if (lane == 0) nlc[vrow] = -lse_row * kLog2e;
     return;
   }
-  const T* po = o + row * d;
-  const T* pd = d_o + row * d;
+  const T* po = o + hb * vo.batch + hh * vo.head + qi * vo.row;
+  const T* pd = d_o + hb * vdo.batch + hh * vdo.head + qi * vdo.row;
   float acc = 0.f;
   for (int c = lane; c < d; c += 32) acc = fmaf(static_cast<float>(po[c]), static_cast<float>(pd[c]), acc);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
     k1[vrow] = -acc;
-    nlc[vrow] = -lse[row] * kLog2e;
+    nlc[vrow] = -lse_row * kLog2e;
   }
 }
 
@@ -95,6 +99,17 @@ int own_status_word(int** out) {
   return FHOB_OK;
 }
 
+// strides of the first `count` matrices of a layout (those given): positive rows, everything 16-byte aligned
+bool layout_ok(const FhobLayout& l, const void* const* mats, int count, size_t es) {
+  const long long align = 16 / static_cast<long long>(es);
+  for (int i = 0; i < count; ++i) {
+    if (!mats[i]) continue;
+    if (l.row[i] <= 0 || l.row[i] % align || l.head[i] % align || l.batch[i] % align || l.head[i] < 0 || l.batch[i] < 0)
+      return false;
+  }
+  return l.lse_head >= 0 && l.lse_batch >= 0;
+}
+
 // `o_optional`: the caller may leave p->o NULL (D is then taken from sum_j P dP inside the sweep
 // that yields dd and b, which only the tensor-core path does)
 int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = true, bool o_optional = false) {
@@ -123,6 +138,14 @@ int validate(const FhobProblem* p, bool need_outputs, bool need_cotangents = tru
   if (p->d > 128 || dv > 128) return FHOB_ERR_SHAPE;
   if (!p->workspace || (reinterpret_cast<uintptr_t>(p->workspace) & 255u)) return FHOB_ERR_WORKSPACE;
   if (p->workspace_bytes < fhob_workspace_bytes(p->bh, p->n_q)) return FHOB_ERR_WORKSPACE;
+  if (p->layout) {
+    // views are read through tensor maps: tensor-core kernels only, strides that keep rows 16-byte aligned
+    const FhobLayout& l = *p->layout;
+    if (l.heads <= 0 || p->bh % l.heads != 0 || l.reserved != 0) return FHOB_ERR_ARG;
+    if (p->impl == FHOB_IMPL_SIMT || !tc_supported(*p)) return FHOB_ERR_SHAPE;
+    const void* mats[8] = {p->q, p->k, p->v, p->o, p->d_o, p->ddq, p->ddk, p->ddv};   // index order of FhobLayout
+    if (!layout_ok(l, mats, need_cotangents ? 8 : 5, es)) return FHOB_ERR_ALIGN;
+  }
   if (p->impl == FHOB_IMPL_TCGEN05 && !tc_supported(*p)) {
     // fp32 with both head dims 64 runs on the tensor cores if the workspace also holds the bf16 hi/lo copies
     if (split_dims_ok(*p)) return FHOB_ERR_WORKSPACE;
@@ -203,18 +226,22 @@ static int run_prepass(const FhobProblem* p, void* stream, bool for_operator = t
   unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
   // bottom-right aligned causal mask: query i sees key 0 only if i + n_k - n_q >= 0
   const int first_live = (p->causal && p->n_q > p->n_k) ? p->n_q - p->n_k : 0;
+  const int dv_ = head_dim_v(*p);
+  const View vo = tensor_view(*p, kTenO, p->n_q, dv_), vdo = tensor_view(*p, kTenDO, p->n_q, dv_);
+  const long long lse_head = p->layout ? p->layout->lse_head : p->n_q;
+  const long long lse_batch = p->layout ? p->layout->lse_batch : static_cast<long long>(p->bh) * p->n_q;
   if (p->dtype == FHOB_BF16) {
     prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
-        rv.status, rows, head_dim_v(*p), p->n_q, first_live);
+        rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
   } else if (p->dtype == FHOB_F16) {
     prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
                                                        static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                       rv.status, rows, head_dim_v(*p), p->n_q, first_live);
+                                                       rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
   } else {
     prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                      rv.status, rows, head_dim_v(*p), p->n_q, first_live);
+                                                      rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
@@ -314,6 +341,14 @@ int fhob_forward(const FhobProblem* p, void* o_out, float* lse_out, void* stream
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tc_ok = aligned16(p->q) && aligned16(p->k) && aligned16(p->v) && aligned16(o_out) &&
                      tc_first_order_supported(*p);
+  if (p->layout) {
+    // views of q, k, v: tensor-core kernels only
+    const FhobLayout& l = *p->layout;
+    if (l.heads <= 0 || p->bh % l.heads != 0 || l.reserved != 0) return FHOB_ERR_ARG;
+    if (p->impl == FHOB_IMPL_SIMT || !tc_ok) return FHOB_ERR_SHAPE;
+    const void* mats[3] = {p->q, p->k, p->v};
+    if (!layout_ok(l, mats, 3, p->dtype == FHOB_F32 ? 4 : 2)) return FHOB_ERR_ALIGN;
+  }
   if (p->impl == FHOB_IMPL_TCGEN05 && !tc_ok) return FHOB_ERR_SHAPE;
   if (p->impl != FHOB_IMPL_SIMT && tc_ok) {
     int* status = static_cast<int*>(p->workspace);

@@ -41,6 +41,39 @@ struct RowVectors {
 // Head dim of V, ddV, dO, O and of the results ddO, dV2 (0 in the struct = same as d).
 inline int head_dim_v(const FhobProblem& p) { return p.d_v > 0 ? p.d_v : p.d; }
 
+// Where the rows of one input matrix are: element strides between rows, between the heads of a
+// batch entry and between batch entries (FhobLayout), or the contiguous (bh, n, d) default.
+// Index order of FhobLayout: q, k, v, o, d_o, ddq, ddk, ddv.
+enum { kTenQ = 0, kTenK = 1, kTenV = 2, kTenO = 3, kTenDO = 4, kTenDDQ = 5, kTenDDK = 6, kTenDDV = 7 };
+struct View {
+  int heads, batches;          // bh = batches * heads
+  long long row, head, batch;  // element strides
+};
+inline View tensor_view(const FhobProblem& p, int which, int n_rows, int d) {
+  View v;
+  if (p.layout) {
+    v.heads = p.layout->heads;
+    v.batches = p.bh / p.layout->heads;
+    v.row = p.layout->row[which];
+    v.head = p.layout->head[which];
+    v.batch = p.layout->batch[which];
+  } else {
+    v.heads = p.bh;
+    v.batches = 1;
+    v.row = d;
+    v.head = static_cast<long long>(n_rows) * d;
+    v.batch = static_cast<long long>(p.bh) * n_rows * d;
+  }
+  return v;
+}
+inline View contiguous_view(int bh, int n_rows, int d) {
+  View v;
+  v.heads = bh; v.batches = 1; v.row = d;
+  v.head = static_cast<long long>(n_rows) * d;
+  v.batch = static_cast<long long>(bh) * n_rows * d;
+  return v;
+}
+
 // Entries per head of a row vector: n_q rounded up to a multiple of four, so that every head's
 // slice (and every 64-query group the key-tiled kernels fetch with a bulk copy) starts on a
 // 16-byte boundary whatever n_q is.

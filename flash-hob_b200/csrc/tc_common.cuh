@@ -112,18 +112,21 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// (bh, n, d) 16-bit row-major tensor, box = 64 columns x `rows` rows of one head, 128-byte swizzle.
+// 16-bit matrix of `n` rows x `d` columns per head, heads and batch entries at the strides of `v`:
+// a 4-D map (d, n, heads, batches), box = 64 columns x `rows` rows of one head, 128-byte swizzle.
 // Encoded maps are kept in a small per-thread table: a training step calls the operator with the
 // same tensors again and again, and an encode costs a few microseconds of host time per map.
 struct MapKey {
   const void* base;
-  int bh, n, d, rows, f16;
+  int n, d, rows, f16, heads, batches;
+  long long row, head, batch;
   bool operator==(const MapKey& o) const {
-    return base == o.base && bh == o.bh && n == o.n && d == o.d && rows == o.rows && f16 == o.f16;
+    return base == o.base && n == o.n && d == o.d && rows == o.rows && f16 == o.f16 && heads == o.heads &&
+           batches == o.batches && row == o.row && head == o.head && batch == o.batch;
   }
 };
 
-int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, bool f16) {
+int make_map(CUtensorMap* m, const void* base, const View& v, int n, int d, int rows, bool f16) {
   constexpr int kSlots = 64;
   struct Entry {
     MapKey key;
@@ -131,7 +134,7 @@ int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, b
   };
   static thread_local Entry table[kSlots];
   static thread_local int used = 0, next = 0;
-  const MapKey key{base, bh, n, d, rows, f16 ? 1 : 0};
+  const MapKey key{base, n, d, rows, f16 ? 1 : 0, v.heads, v.batches, v.row, v.head, v.batch};
   for (int i = 0; i < used; ++i)
     if (table[i].key == key) {
       *m = table[i].map;
@@ -142,11 +145,15 @@ int make_map(CUtensorMap* m, const void* base, int bh, int n, int d, int rows, b
     set_cuda_error_text("cuTensorMapEncodeTiled entry point not available");
     return FHOB_ERR_CUDA;
   }
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(bh)};
-  cuuint64_t strides[2] = {static_cast<cuuint64_t>(d) * 2, static_cast<cuuint64_t>(n) * d * 2};
-  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(rows), 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  // strides of the three outer dims in bytes: multiples of 16, checked by the caller's validation
+  // and once more by the driver
+  cuuint64_t dims[4] = {static_cast<cuuint64_t>(d), static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(v.heads),
+                        static_cast<cuuint64_t>(v.batches)};
+  cuuint64_t strides[3] = {static_cast<cuuint64_t>(v.row) * 2, static_cast<cuuint64_t>(v.head) * 2,
+                           static_cast<cuuint64_t>(v.batch) * 2};
+  cuuint32_t box[4] = {64, static_cast<cuuint32_t>(rows), 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(m, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {

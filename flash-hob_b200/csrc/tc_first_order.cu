@@ -73,6 +73,7 @@ struct FoParams {
   uint16_t* out1;     // BK: dV
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
+  int heads;            // heads per batch entry of the input tensor maps (4-D: columns, rows, head, batch)
   int d_out0, d_out1;   // columns of the results in memory (<= the tile widths; see fo_launch)
   float scale;
 };
@@ -181,12 +182,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
   if (warp == TMA_WARP) {
     // ================================================= TMA producer
     if (lane == 0 && n_iter > 0) {
+      const int head_b = head / p.heads, head_h = head - head_b * p.heads;   // batch entry and head within it
       mbar_arrive_expect_tx(&bars->stat_full, C::STAT_BYTES);
 #pragma unroll
       for (int i = 0; i < C::NSTAT; ++i)
         for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
-          tma_load_3d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
-                      head);
+          tma_load_4d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
+                      head_h, head_b);
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
         const int slot = it % C::NSLOT;
@@ -197,8 +199,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) fo_kernel(const __grid_constant__
 #pragma unroll
         for (int i = 0; i < C::NSTRM; ++i)
           for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
-            tma_load_3d(dst + C::strm_off(i) + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
-                        head);
+            tma_load_4d(dst + C::strm_off(i) + bx * (BN * 128), &p.strm[i], &bars->strm_full[slot], bx * 64, n0,
+                        head_h, head_b);
         if (MODE == FO_BK) {
           const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
           uint8_t* sv = dst + C::STRM_BYTES;
@@ -689,19 +691,25 @@ int fo_launch(const FhobProblem& p, FoParams& tp, cudaStream_t s) {
   }
   // head dims below the tile widths: the boxes reach past the end of a row and are zero-filled there
   const int d_mem[2] = {SPLIT ? 128 : p.d, SPLIT ? 128 : head_dim_v(p)};
+  // where each input lives: the caller's layout, or contiguous (always so for the split copies)
+  const int q_ids[2] = {kTenQ, kTenDO}, k_ids[2] = {kTenK, kTenV};
+  auto view = [&](int id, int n_rows, int d) {
+    return SPLIT ? contiguous_view(p.bh, n_rows, d) : tensor_view(p, id, n_rows, d);
+  };
   int st = FHOB_OK;
   if (MODE != FO_BK) {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, d_mem[i], BM, F16);
+      st = make_map(&tp.stat[i], q_side[i], view(q_ids[i], p.n_q, d_mem[i]), p.n_q, d_mem[i], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, d_mem[i], C::BN, F16);
+      st = make_map(&tp.strm[i], k_side[i], view(k_ids[i], p.n_k, d_mem[i]), p.n_k, d_mem[i], C::BN, F16);
   } else {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, d_mem[i], BM, F16);
+      st = make_map(&tp.stat[i], k_side[i], view(k_ids[i], p.n_k, d_mem[i]), p.n_k, d_mem[i], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i], C::BN, F16);
+      st = make_map(&tp.strm[i], q_side[i], view(q_ids[i], p.n_q, d_mem[i]), p.n_q, d_mem[i], C::BN, F16);
   }
   if (st != FHOB_OK) return st;
+  tp.heads = (!SPLIT && p.layout) ? p.layout->heads : p.bh;
   tp.d_out0 = MODE == FO_ONE ? head_dim_v(p) : p.d;   // columns in memory of O | dQ | dK
   tp.d_out1 = head_dim_v(p);                          // dV
   tp.n_q = p.n_q; tp.n_k = p.n_k; tp.causal = p.causal; tp.window = p.window; tp.scale = p.scale;

@@ -108,6 +108,7 @@ struct TcParams {
   uint16_t* out1;
   int* status;
   int n_q, n_k, causal, window, tiles_per_head;
+  int heads;            // heads per batch entry of the input tensor maps (4-D: columns, rows, head, batch)
   int d_out0, d_out1;   // columns of the two results in memory (<= the tile widths DQK, DV; see launch)
   float scale;
 };
@@ -442,12 +443,13 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
   if (warp == TMA_WARP) {
     // ================================================= TMA producer
     if (lane == 0 && n_iter > 0) {
+      const int head_b = head / p.heads, head_h = head - head_b * p.heads;   // batch entry and head within it
       mbar_arrive_expect_tx(&bars->stat_full, C::STAT_BYTES);
 #pragma unroll
       for (int i = 0; i < C::NSTAT; ++i)
         for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
-          tma_load_3d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
-                      head);
+          tma_load_4d(stat_tiles + C::stat_off(i) + bx * (BM * 128), &p.stat[i], &bars->stat_full, bx * 64, m0,
+                      head_h, head_b);
       int issued = 0;
       for (int it = 0; it < n_iter; ++it) {
         const int slot = it % C::NSLOT;
@@ -458,8 +460,8 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 #pragma unroll
         for (int i = 0; i < C::NSTRM; ++i)
           for (int bx = 0; bx < C::tile_d(i) / 64; ++bx)
-            tma_load_3d(dst + C::strm_base(i) + bx * C::strm_box(i), &p.strm[i], &bars->strm_full[slot], bx * 64,
-                        n0, head);
+            tma_load_4d(dst + C::strm_base(i) + bx * C::strm_box(i), &p.strm[i], &bars->strm_full[slot], bx * 64,
+                        n0, head_h, head_b);
         if (PASS == 4) {
           const size_t vo = static_cast<size_t>(head) * row_stride(p.n_q) + n0;
           uint8_t* sv = dst + C::STRM_BYTES;
@@ -861,12 +863,15 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 
 // fp32 rows of d <= 64 columns -> [hi(64) | lo(64)] bf16 rows (see split_pack), zero beyond d: one
 // thread per pair of columns of the 64-wide row.
-__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs, int d) {
+__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs, int d,
+                                  int n_rows, View v) {
   const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= pairs) return;
-  const long row = i >> 5;          // 32 pairs of columns per row of 64
+  const long row = i >> 5;          // 32 pairs of columns per row of 64; rows of the copy are dense (bh, n, 128)
   const int c2 = static_cast<int>(i & 31);
-  const float2 x = 2 * c2 < d ? *reinterpret_cast<const float2*>(src + row * d + 2 * c2) : make_float2(0.f, 0.f);
+  const long bh = row / n_rows, r = row - bh * n_rows;
+  const float* s = src + (bh / v.heads) * v.batch + (bh % v.heads) * v.head + r * v.row;   // the source may be a view
+  const float2 x = 2 * c2 < d ? *reinterpret_cast<const float2*>(s + 2 * c2) : make_float2(0.f, 0.f);
   uint32_t hi, lo;
   split_pack(x.x, x.y, hi, lo);
   dst[row * 64 + c2] = hi;          // a split row is 128 bf16 = 64 words: hi in words [0, 32), lo in [32, 64)
@@ -892,19 +897,25 @@ int launch(const FhobProblem& p, cudaStream_t s) {
   // tensor map: the 64-column boxes reach past the end of a row, the TMA unit fills those columns
   // with zeros, zeros add nothing to a contraction, and the epilogue stores only the columns that exist.
   const int d_mem[2] = {SPLIT ? 128 : p.d, SPLIT ? 128 : head_dim_v(p)};   // columns in memory of the two tile kinds
+  // where each input lives: the caller's layout, or contiguous (always so for the split copies)
+  const int q_ids[3] = {kTenQ, kTenDDQ, kTenDO}, k_ids[4] = {kTenK, kTenDDK, kTenV, kTenDDV};
+  auto view = [&](int id, int n_rows, int d) {
+    return SPLIT ? contiguous_view(p.bh, n_rows, d) : tensor_view(p, id, n_rows, d);
+  };
   int st = FHOB_OK;
   if (PASS != 4) {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], q_side[i], p.bh, p.n_q, d_mem[i < 2 ? 0 : 1], BM, F16);
+      st = make_map(&tp.stat[i], q_side[i], view(q_ids[i], p.n_q, d_mem[i < 2 ? 0 : 1]), p.n_q, d_mem[i < 2 ? 0 : 1], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], k_side[i], p.bh, p.n_k, d_mem[i < 2 ? 0 : 1], BN, F16);
+      st = make_map(&tp.strm[i], k_side[i], view(k_ids[i], p.n_k, d_mem[i < 2 ? 0 : 1]), p.n_k, d_mem[i < 2 ? 0 : 1], BN, F16);
   } else {
     for (int i = 0; i < C::NSTAT && st == FHOB_OK; ++i)
-      st = make_map(&tp.stat[i], k_side[i], p.bh, p.n_k, d_mem[i < 2 ? 0 : 1], BM, F16);
+      st = make_map(&tp.stat[i], k_side[i], view(k_ids[i], p.n_k, d_mem[i < 2 ? 0 : 1]), p.n_k, d_mem[i < 2 ? 0 : 1], BM, F16);
     for (int i = 0; i < C::NSTRM && st == FHOB_OK; ++i)
-      st = make_map(&tp.strm[i], q_side[i], p.bh, p.n_q, d_mem[i < 2 ? 0 : 1], BN, F16);
+      st = make_map(&tp.strm[i], q_side[i], view(q_ids[i], p.n_q, d_mem[i < 2 ? 0 : 1]), p.n_q, d_mem[i < 2 ? 0 : 1], BN, F16);
   }
   if (st != FHOB_OK) return st;
+  tp.heads = (!SPLIT && p.layout) ? p.layout->heads : p.bh;
   tp.d_out0 = p.d;               // columns of the results in memory (split operands: up to 64 fp32 columns)
   tp.d_out1 = head_dim_v(p);
   tp.nlc = rv.nlc; tp.k1 = rv.k1; tp.ndd = rv.ndd; tp.k23 = rv.k23;
@@ -982,15 +993,18 @@ int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which) {
   if (!tc_split_supported(p)) return FHOB_ERR_SHAPE;
   SplitBuffers sb = split_buffers(p);
   const void* src[7] = {p.q, p.ddq, p.d_o, p.k, p.ddk, p.v, p.ddv};   // bit i of `which` = tensor i
+  const int ids[7] = {kTenQ, kTenDDQ, kTenDO, kTenK, kTenDDK, kTenV, kTenDDV};
   void* dst[7] = {sb.q, sb.ddq, sb.d_o, sb.k, sb.ddk, sb.v, sb.ddv};
   for (int i = 0; i < 7; ++i) {
     if (!(which & (1 << i))) continue;
     if (!src[i]) return FHOB_ERR_ARG;
-    const long rows = static_cast<long>(p.bh) * (i < 3 ? p.n_q : p.n_k);
-    const long pairs = rows * 32;
+    const int n_rows = i < 3 ? p.n_q : p.n_k;
+    const long pairs = static_cast<long>(p.bh) * n_rows * 32;
     const bool v_side = i == 2 || i >= 5;   // dO, V, ddV
+    const int d = v_side ? head_dim_v(p) : p.d;
     split_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(
-        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs, v_side ? head_dim_v(p) : p.d);
+        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs, d, n_rows,
+        tensor_view(p, ids[i], n_rows, d));
     FHOB_CUDA_OK(cudaGetLastError());
   }
   return FHOB_OK;

@@ -22,6 +22,15 @@ SYMBOLS = (
 STATIC_SCRATCH_MAX_ROWS = 262144
 
 
+class FhobLayout(C.Structure):
+    """Element strides of q, k, v, o, d_o, ddq, ddk, ddv (rows / heads of a batch entry / batch entries) and of lse."""
+    _fields_ = [
+        ("heads", C.c_int32), ("reserved", C.c_int32),
+        ("row", C.c_int64 * 8), ("head", C.c_int64 * 8), ("batch", C.c_int64 * 8),
+        ("lse_head", C.c_int64), ("lse_batch", C.c_int64),
+    ]
+
+
 class FhobProblem(C.Structure):
     _fields_ = [
         ("bh", C.c_int32), ("n_q", C.c_int32), ("n_k", C.c_int32), ("d", C.c_int32),
@@ -31,6 +40,7 @@ class FhobProblem(C.Structure):
         ("ddq", C.c_void_p), ("ddk", C.c_void_p), ("ddv", C.c_void_p), ("lse", C.c_void_p),
         ("dq2", C.c_void_p), ("dk2", C.c_void_p), ("dv2", C.c_void_p), ("ddo", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("layout", C.POINTER(FhobLayout)),
     ]
 
 

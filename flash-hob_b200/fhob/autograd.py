@@ -33,12 +33,19 @@ def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sli
     """
     # the problem struct wants three cotangent tensors of the right shapes; they are not read
     prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, impl, need_outputs=False, window=sliding_window)
-    q, k, v = prob.keep[0], prob.keep[1], prob.keep[2]
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (Q, K, V))   # contiguous results
+    lib = _lib.load()
     with torch.cuda.device(prob.device):
-        _lib.check(_lib.load().fhob_backward(C.byref(prob.p), C.c_void_p(dq.data_ptr()), C.c_void_p(dk.data_ptr()),
-                                             C.c_void_p(dv.data_ptr()), C.c_void_p(prob.stream)), "fhob_backward")
-    return dq.reshape(Q.shape), dk.reshape(K.shape), dv.reshape(V.shape)
+        call = lambda pr: lib.fhob_backward(C.byref(pr.p), C.c_void_p(dq.data_ptr()), C.c_void_p(dk.data_ptr()),
+                                            C.c_void_p(dv.data_ptr()), C.c_void_p(pr.stream))
+        rc = call(prob)
+        if rc != 0 and prob.layout is not None:
+            # a view the tensor-map encoder does not take: read copies instead
+            prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, impl, need_outputs=False,
+                            window=sliding_window, allow_views=False)
+            rc = call(prob)
+        _lib.check(rc, "fhob_backward")
+    return dq, dk, dv
 
 
 class _AttentionBackward(torch.autograd.Function):

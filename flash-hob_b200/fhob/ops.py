@@ -39,6 +39,37 @@ def _fold(t: torch.Tensor, name: str) -> torch.Tensor:
     return t.contiguous()
 
 
+def _tc_capable(dtype: torch.dtype, d: int, d_v: int) -> bool:
+    """Shapes the tensor-core kernels take (they are the ones that read views through tensor maps)."""
+    if dtype == torch.float32:
+        return d <= 64 and d_v <= 64 and d % 4 == 0 and d_v % 4 == 0
+    return d <= 128 and d_v <= 128 and d % 8 == 0 and d_v % 8 == 0
+
+
+def _strides_of(t: torch.Tensor, batches: int, heads: int):
+    """(row, head, batch) element strides of a (BH, N, D) or (B, H, N, D) tensor over the common
+    (batches, heads) split of the folded axis, or None when the tensor cannot be read in place:
+    last dim not contiguous, a stride or the base address off the 16-byte grid, heads of the folded
+    axis not equally spaced."""
+    align = 16 // t.element_size()
+    if t.data_ptr() % 16 or (t.shape[-1] > 1 and t.stride(-1) != 1):
+        return None
+    if t.dim() == 4:
+        if tuple(t.shape[:2]) != (batches, heads):
+            return None
+        batch, head, row = t.stride(0), t.stride(1), t.stride(2)
+    else:
+        if t.shape[0] != batches * heads:
+            return None
+        head, row = t.stride(0), t.stride(1)
+        batch = head * heads
+    if t.shape[-2] == 1:
+        row = t.shape[-1]          # a single row: any positive stride describes it
+    if row <= 0 or head < 0 or batch < 0 or row % align or head % align or batch % align:
+        return None
+    return row, head, batch
+
+
 def _window(is_causal, sliding_window) -> int:
     """0 for no window, else the validated sliding_window_length."""
     if sliding_window is None or sliding_window == float("inf"):
@@ -55,7 +86,7 @@ class _Problem:
     """Validated tensors + the FhobProblem struct that points at them."""
 
     def __init__(self, Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, need_outputs=True,
-                 window=None, out=None, workspace=None):
+                 window=None, out=None, workspace=None, allow_views=True):
         names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
         no_o = O is None
         if no_o:
@@ -77,7 +108,25 @@ class _Problem:
             if t.dtype != dt:
                 raise TypeError(f"{n} has dtype {t.dtype}, Q has {dt}")
         self.out_shapes = (Q.shape, K.shape, V.shape, dO.shape)   # dQ2, dK2, dV2, ddO
-        t3 = [_fold(t, n) for n, t in zip(names, tensors)]
+        for n, t in zip(names, tensors):
+            if t.dim() not in (3, 4):
+                raise ValueError(f"{n}: expected (BH, N, D) or (B, H, N, D), got {tuple(t.shape)}")
+        # Views (a (B, N, H, D) projection seen as (B, H, N, D), a slice of a fused QKV tensor, ...)
+        # are read in place through tensor maps when the tensor-core kernels run and every stride
+        # stays on the 16-byte grid; anything else is made contiguous first (a copy).
+        batches, heads = (Q.shape[0], Q.shape[1]) if Q.dim() == 4 else (1, Q.shape[0])
+        strides = None
+        if (allow_views and impl != "simt" and _tc_capable(dt, Q.shape[-1], V.shape[-1])
+                and not all(t.is_contiguous() for t in tensors)):
+            strides = [_strides_of(t, batches, heads) for t in tensors]
+            if any(st is None for st in strides):
+                strides = None
+        if strides is None:
+            t3 = [_fold(t, n) for n, t in zip(names, tensors)]
+        else:
+            # shape-only stand-ins (folded) for the checks below; the kernels read `tensors` in place
+            t3 = [torch.empty((t.shape[0] if t.dim() == 3 else t.shape[0] * t.shape[1], t.shape[-2], t.shape[-1]),
+                              dtype=dt, device="meta") for t in tensors]
         q, k, v, o, do, ddq, ddk, ddv = t3
         bh, n_q, d = q.shape
         n_k, d_v = k.shape[1], v.shape[2]
@@ -91,7 +140,7 @@ class _Problem:
         if tuple(lse.shape) != (bh, n_q) or L.device != dev:
             raise ValueError(f"L: expected {(bh, n_q)} on {dev}, got {tuple(L.shape)} on {L.device}")
         lse = lse.to(torch.float32).contiguous()
-        self.keep = t3 + [lse]
+        self.keep = (t3 if strides is None else tensors) + [lse]
         self.device = dev
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         lib = _lib.load()
@@ -114,12 +163,23 @@ class _Problem:
                 raise ValueError(f"workspace: need a contiguous uint8 tensor of at least {nbytes} bytes on {dev}, "
                                  "256-byte aligned")
             self.ws = workspace
-        p.q, p.k, p.v, p.o, p.d_o = (t.data_ptr() for t in (q, k, v, o, do))
+        src = tensors if strides is not None else t3      # views: the caller's tensors, read in place
+        p.q, p.k, p.v, p.o, p.d_o, p.ddq, p.ddk, p.ddv = (t.data_ptr() for t in src)
         if no_o:
             p.o = None
-        p.ddq, p.ddk, p.ddv, p.lse = (t.data_ptr() for t in (ddq, ddk, ddv, lse))
+        p.lse = lse.data_ptr()
+        self.layout = None
+        if strides is not None:
+            lay = _lib.FhobLayout()
+            lay.heads = heads
+            for i, (row, head, batch) in enumerate(strides):
+                lay.row[i], lay.head[i], lay.batch[i] = row, head, batch
+            lay.lse_head, lay.lse_batch = n_q, heads * n_q
+            self.layout = lay                              # kept alive with the problem
+            p.layout = C.pointer(lay)
         if need_outputs and out is not None:
-            want = (q.shape, k.shape, v.shape, do.shape)
+            want = (torch.Size((bh, n_q, d)), torch.Size((bh, n_k, d)), torch.Size((bh, n_k, d_v)),
+                    torch.Size((bh, n_q, d_v)))
             if len(out) != 4:
                 raise ValueError("out: expected (dQ2, dK2, dV2, ddO)")
             folded = []
@@ -130,8 +190,9 @@ class _Problem:
             self.dq2, self.dk2, self.dv2, self.ddo = folded
             p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
         elif need_outputs:
-            self.dq2, self.ddo = torch.empty_like(q), torch.empty_like(do)
-            self.dk2, self.dv2 = torch.empty_like(k), torch.empty_like(v)
+            new = lambda n, w: torch.empty(bh, n, w, dtype=dt, device=dev)   # results are always contiguous
+            self.dq2, self.ddo = new(n_q, d), new(n_q, d_v)
+            self.dk2, self.dv2 = new(n_k, d), new(n_k, d_v)
             p.dq2, p.dk2, p.dv2, p.ddo = (t.data_ptr() for t in (self.dq2, self.dk2, self.dv2, self.ddo))
         p.workspace, p.workspace_bytes = self.ws.data_ptr(), self.ws.numel()
         self.p = p
@@ -151,7 +212,13 @@ def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check,
                     workspace=workspace)
     lib = _lib.load()
     with torch.cuda.device(prob.device):
-        _lib.check(lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream)), "fhob_bwdbwd")
+        rc = lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream))
+        if rc != 0 and prob.layout is not None:
+            # a view the driver's tensor-map encoder (or the library) does not take: fall back to copies
+            prob = _Problem(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, window=window, out=out,
+                            workspace=workspace, allow_views=False)
+            rc = lib.fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream))
+        _lib.check(rc, "fhob_bwdbwd")
         if check:
             _lib.check(prob.status(), "fhob_bwdbwd (device status)")
     return prob.outputs()
@@ -250,7 +317,11 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     n_chunks = max(-(-bh // per_range), min(bh, 4))
     bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
     widest = max(hi - lo for lo, hi in zip(bounds, bounds[1:]))
-    ws = _workspace(dev, main.cuda_stream, _lib.load().fhob_workspace_bytes(widest, mats3[0].shape[1]))
+    sizing = _lib.FhobProblem()       # the widest range decides the workspace (fp32: room for the bf16 copies too)
+    sizing.bh, sizing.n_q, sizing.n_k, sizing.d = widest, mats3[0].shape[1], mats3[1].shape[1], mats3[0].shape[2]
+    sizing.d_v = 0 if mats3[2].shape[2] == mats3[0].shape[2] else mats3[2].shape[2]
+    sizing.dtype, sizing.impl = _lib.DTYPES[str(mats3[0].dtype)], _lib.IMPL[impl]
+    ws = _workspace(dev, main.cuda_stream, _lib.load().fhob_workspace_bytes_problem(C.byref(sizing)))
     # the pre-pass of every range clears the status word, so each range's word is kept
     status_host = torch.zeros(n_chunks, dtype=torch.int32, pin_memory=True) if check else None
     for i, (lo, hi) in enumerate(zip(bounds, bounds[1:])):
@@ -296,36 +367,63 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
     Queries that see no key (causal with N_K < N_Q) get ``O = 0``, ``L = -inf``.
     """
     shape_q = Q.shape
-    q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
-    if q.device.type != "cuda" or str(q.dtype) not in _lib.DTYPES:
+    if Q.device.type != "cuda" or str(Q.dtype) not in _lib.DTYPES:
         raise ValueError("attention_forward needs CUDA bfloat16/float16/float32 tensors")
+    if impl not in _lib.IMPL:
+        raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
+    # views are read in place when the tensor-core kernels run (see _Problem); else folded copies
+    strides = None
+    if (all(t.dim() in (3, 4) for t in (Q, K, V)) and impl != "simt" and _tc_capable(Q.dtype, Q.shape[-1], V.shape[-1])
+            and not all(t.is_contiguous() for t in (Q, K, V))):
+        batches, heads = (Q.shape[0], Q.shape[1]) if Q.dim() == 4 else (1, Q.shape[0])
+        strides = [_strides_of(t, batches, heads) for t in (Q, K, V)]
+        if any(st is None for st in strides):
+            strides = None
+    if strides is None:
+        q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
+    else:
+        q, k, v = (torch.empty((t.shape[0] if t.dim() == 3 else t.shape[0] * t.shape[1], t.shape[-2], t.shape[-1]),
+                               dtype=t.dtype, device="meta") for t in (Q, K, V))
     bh, n_q, d = q.shape
     d_v = v.shape[2]
     if k.shape != (bh, k.shape[1], d) or v.shape[:2] != k.shape[:2]:
         raise ValueError(f"K {tuple(k.shape)} / V {tuple(v.shape)} do not match Q {tuple(q.shape)}")
     if scale is None:
         scale = d ** -0.5
-    o = torch.empty(bh, n_q, d_v, dtype=q.dtype, device=q.device) if need_o else None
-    lse = torch.empty(bh, n_q, dtype=torch.float32, device=q.device)
+    o = torch.empty(bh, n_q, d_v, dtype=Q.dtype, device=Q.device) if need_o else None
+    lse = torch.empty(bh, n_q, dtype=torch.float32, device=Q.device)
     p = _lib.FhobProblem()
     p.bh, p.n_q, p.n_k, p.d = bh, n_q, k.shape[1], d
     p.d_v = 0 if d_v == d else d_v
-    p.dtype = _lib.DTYPES[str(q.dtype)]
-    if impl not in _lib.IMPL:
-        raise ValueError(f"impl must be one of {sorted(_lib.IMPL)}, got {impl!r}")
+    p.dtype = _lib.DTYPES[str(Q.dtype)]
     p.causal, p.impl, p.scale = (1 if is_causal else 0), _lib.IMPL[impl], float(scale)
     p.window = _window(is_causal, sliding_window)
-    p.q, p.k, p.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
-    stream = torch.cuda.current_stream(q.device).cuda_stream
+    src = (Q, K, V) if strides is not None else (q, k, v)
+    p.q, p.k, p.v = (t.data_ptr() for t in src)
+    lay = None
+    if strides is not None:
+        lay = _lib.FhobLayout()
+        lay.heads = Q.shape[1] if Q.dim() == 4 else bh
+        for i, (row, head, batch) in enumerate(strides):
+            lay.row[i], lay.head[i], lay.batch[i] = row, head, batch
+        p.layout = C.pointer(lay)
+    stream = torch.cuda.current_stream(Q.device).cuda_stream
     lib = _lib.load()
     # receives the status word; fp32 with head dim 64: also the bf16 hi/lo copies of the inputs that
     # let the problem run on the tensor cores
     p.n_k = k.shape[1]
-    ws = _workspace(q.device, stream, max(256, lib.fhob_workspace_bytes_problem(C.byref(p))))
+    ws = _workspace(Q.device, stream, max(256, lib.fhob_workspace_bytes_problem(C.byref(p))))
     p.workspace, p.workspace_bytes = ws.data_ptr(), ws.numel()
-    with torch.cuda.device(q.device):
-        _lib.check(lib.fhob_forward(C.byref(p), C.c_void_p(o.data_ptr() if need_o else None),
-                                    C.c_void_p(lse.data_ptr()), C.c_void_p(stream)), "fhob_forward")
+    with torch.cuda.device(Q.device):
+        call = lambda: lib.fhob_forward(C.byref(p), C.c_void_p(o.data_ptr() if need_o else None),
+                                        C.c_void_p(lse.data_ptr()), C.c_void_p(stream))
+        rc = call()
+        if rc != 0 and lay is not None:
+            # a view the tensor-map encoder does not take: read copies instead
+            q, k, v = _fold(Q, "Q"), _fold(K, "K"), _fold(V, "V")
+            p.q, p.k, p.v, p.layout = q.data_ptr(), k.data_ptr(), v.data_ptr(), None
+            rc = call()
+        _lib.check(rc, "fhob_forward")
         if check:
             _lib.check(lib.fhob_read_status(C.byref(p), C.c_void_p(stream)), "fhob_forward (device status)")
     return (o.reshape(*shape_q[:-1], d_v) if need_o else None), lse.reshape(shape_q[:-1])

@@ -55,6 +55,28 @@ enum {
 };
 
 /*
+ * Optional memory layout of the eight matrices and of lse, for callers whose
+ * tensors are views (a (B, N, H, D) projection seen as (B, H, N, D), a slice
+ * of a fused QKV tensor, ...).  The reference passes the strides of every
+ * tensor to its kernels (fhog/triton_bwdbwd.py:594-610, :628-640); this is the
+ * same information.  Strides are in elements; the last dim (d) is contiguous.
+ * Head bh of the folded axis is (batch b, head h) = (bh / heads, bh % heads).
+ * Index order of the arrays: q, k, v, o, d_o, ddq, ddk, ddv.
+ * Only the tensor-core kernels take a layout (impl AUTO resolving to them, or
+ * TCGEN05); every stride must keep rows 16-byte aligned.  Results are always
+ * written contiguous (bh, n, d).
+ */
+typedef struct FhobLayout {
+  int32_t heads;       /* heads per batch entry; bh must be a multiple of it */
+  int32_t reserved;    /* must be 0 */
+  int64_t row[8];      /* stride between consecutive rows of a head */
+  int64_t head[8];     /* stride between the heads of one batch entry */
+  int64_t batch[8];    /* stride between batch entries */
+  int64_t lse_head;    /* lse (rows contiguous): stride between heads ... */
+  int64_t lse_batch;   /* ... and between batch entries */
+} FhobLayout;
+
+/*
  * One double-backward problem.  Replaces the argument list of
  * flash_bwdbwd (fhog/triton_bwdbwd.py:558) and of its two kernel launches
  * (fhog/triton_bwdbwd.py:586-612, :620-646).
@@ -95,6 +117,8 @@ typedef struct FhobProblem {
   /* scratch: fhob_workspace_bytes(bh, n_q) bytes, 256-byte aligned */
   void* workspace;
   size_t workspace_bytes;
+  /* NULL = every matrix contiguous (bh, n, d) and lse contiguous (bh, n_q); see FhobLayout */
+  const struct FhobLayout* layout;
 } FhobProblem;
 
 /* Library version (major*10000 + minor*100 + patch). */

@@ -34,8 +34,16 @@ def test_exports_every_declared_symbol(lib):
 def test_struct_matches_header(lib):
     header = (ROOT / "include" / "fhob.h").read_text()
     body = header.split("typedef struct FhobProblem {")[1].split("} FhobProblem;")[0]
-    fields = re.findall(r"^\s*(?:const\s+)?[a-z0-9_]+\*?\s+\*?([a-z0-9_]+);", body, flags=re.M)
+    fields = re.findall(r"^\s*(?:const\s+)?(?:struct\s+)?[A-Za-z0-9_]+\*?\s+\*?([a-z0-9_]+);", body, flags=re.M)
     assert fields == [f[0] for f in _lib.FhobProblem._fields_]
+
+
+def test_layout_struct_matches_header(lib):
+    header = (ROOT / "include" / "fhob.h").read_text()
+    body = header.split("typedef struct FhobLayout {")[1].split("} FhobLayout;")[0]
+    fields = re.findall(r"^\s*[a-z0-9_]+\s+([a-z0-9_]+)(?:\[8\])?;", body, flags=re.M)
+    assert fields == [f[0] for f in _lib.FhobLayout._fields_]
+    assert C.sizeof(_lib.FhobLayout) == 8 + 3 * 8 * 8 + 16
 
 
 def test_workspace_is_linear_in_rows(lib):
@@ -73,6 +81,35 @@ def test_bad_problems_are_rejected_before_launch(lib, over, code):
     p = _problem(**over)
     assert lib.fhob_bwdbwd(C.byref(p), None) == code
     assert lib.fhob_strerror(code) != b"unknown status"
+
+
+def test_bad_layouts_are_rejected_before_launch(lib):
+    def with_layout(**over):
+        lay = _lib.FhobLayout()
+        lay.heads = 2
+        for i in range(8):
+            lay.row[i], lay.head[i], lay.batch[i] = 128, 64, 128 * 256
+        lay.lse_head, lay.lse_batch = 128, 256
+        for k, v in over.items():
+            if isinstance(v, tuple):
+                getattr(lay, k)[v[0]] = v[1]
+            else:
+                setattr(lay, k, v)
+        return lay
+    cases = [(dict(heads=0), 1), (dict(heads=3), 1), (dict(reserved=1), 1), (dict(row=(1, 124)), 3), (dict(row=(0, 0)), 3),
+             (dict(head=(2, 4)), 3), (dict(batch=(7, -8)), 3), (dict(lse_head=-1), 3)]
+    for over, code in cases:
+        lay = with_layout(**over)
+        p = _problem()
+        p.layout = C.pointer(lay)
+        assert lib.fhob_bwdbwd(C.byref(p), None) == code, over
+    lay = with_layout()
+    p = _problem(impl=1)                    # views need the tensor-core kernels
+    p.layout = C.pointer(lay)
+    assert lib.fhob_bwdbwd(C.byref(p), None) == 2
+    p = _problem(dtype=1, d=128)            # fp32 at head dim 128 runs on CUDA cores: no views
+    p.layout = C.pointer(lay)
+    assert lib.fhob_bwdbwd(C.byref(p), None) == 2
 
 
 def test_null_problem(lib):

@@ -938,6 +938,65 @@ def test_head_dims_that_are_not_64_or_128_on_the_tensor_cores(bh, nq, nk, dqk, d
         assert g.shape == r.shape and O.rel_err(g, r) < TOL_BF16, n
 
 
+def _as_views(x, b, h, kind):
+    """The same values as `x` ((b*h, n, d) tensors) behind non-contiguous memory layouts."""
+    out = {}
+    for n, t in x.items():
+        bh, rows, d = t.shape
+        t4 = t.reshape(b, h, rows, d)
+        if kind == "bnhd":          # (B, N, H, D) memory seen as (B, H, N, D)
+            out[n] = t4.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+        elif kind == "padded":      # rows with padding behind them (a slice of a wider projection), folded 3-D
+            wide = torch.zeros(bh, rows, d + 24, dtype=t.dtype, device=t.device)
+            wide[..., :d] = t
+            out[n] = wide[..., :d]
+        elif kind == "hbnd":        # (H, B, N, D) memory seen as (B, H, N, D)
+            out[n] = t4.permute(1, 0, 2, 3).contiguous().permute(1, 0, 2, 3)
+        assert not out[n].is_contiguous() and torch.equal(out[n].reshape(bh, rows, d), t)
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("kind", ["bnhd", "padded", "hbnd"])
+def test_views_are_read_in_place(kind, dtype):
+    """Non-contiguous inputs (the reference passes every tensor's strides to its kernels,
+    fhog/triton_bwdbwd.py:594-610): read through tensor maps without a copy, same bits as the
+    contiguous call, for the operator, the forward and the first backward."""
+    import fhob
+    from fhob.ops import _Problem
+    b, h, nq, nk, d = 2, 3, 200, 328, 64
+    x = make_inputs(b * h, nq, nk, d, seed=451, dtype=dtype, device="cuda")
+    scale = d ** -0.5
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=True)
+    args = (x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale)
+    want = fhob.flash_bwdbwd(*args, is_causal=True, check=True)
+    xv = _as_views(dict(x, o=o), b, h, kind)
+    lse_v = lse if kind == "padded" else lse.reshape(b, h, nq)
+    vargs = (xv["q"], xv["k"], xv["v"], xv["o"], xv["do"], xv["ddq"], xv["ddk"], xv["ddv"], lse_v, scale)
+    prob = _Problem(*vargs, True, "auto")
+    assert prob.layout is not None and prob.p.q == xv["q"].data_ptr()       # the caller's memory, no copy
+    from fhob import _lib
+    import ctypes as C
+    assert _lib.load().fhob_bwdbwd(C.byref(prob.p), C.c_void_p(prob.stream)) == 0   # the library takes the layout
+    assert prob.status() == 0
+    for n, g, w in zip(OUT_NAMES, prob.outputs(), want):
+        assert torch.equal(g.reshape(w.shape), w), n
+    got = fhob.flash_bwdbwd(*vargs, is_causal=True, check=True)
+    for n, g, w in zip(OUT_NAMES, got, want):
+        assert g.is_contiguous() and torch.equal(g.reshape(w.shape), w), n
+    o2, lse2 = fhob.attention_forward(xv["q"], xv["k"], xv["v"], scale, is_causal=True, check=True)
+    assert torch.equal(o2.reshape(o.shape), o) and torch.equal(lse2.reshape(lse.shape), lse)
+    first_w = fhob.attention_backward(x["q"], x["k"], x["v"], o, x["do"], lse, scale, is_causal=True)
+    first = fhob.attention_backward(xv["q"], xv["k"], xv["v"], xv["o"], xv["do"], lse_v, scale, is_causal=True)
+    for g, w in zip(first, first_w):
+        assert torch.equal(g.reshape(w.shape), w)
+    # the CUDA-core kernels do not take views: the wrapper copies, results unchanged
+    sim_w = fhob.flash_bwdbwd(*args, is_causal=True, impl="simt", check=True)
+    sim = fhob.flash_bwdbwd(*vargs, is_causal=True, impl="simt", check=True)
+    for g, w in zip(sim, sim_w):
+        assert torch.equal(g.reshape(w.shape), w)
+
+
 def test_preallocated_outputs_and_workspace():
     """out= and workspace=: the call writes into the caller's tensors and allocates nothing."""
     import fhob
