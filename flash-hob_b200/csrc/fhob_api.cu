@@ -22,46 +22,61 @@ void set_cuda_error_text(const char* text) { std::snprintf(g_cuda_error, sizeof(
 
 namespace {
 
-// One warp per query row: D = sum_d dO*O, stored as k1 = -D, and nlc = -L*log2(e).
+// A group of `lanes` lanes (a power of two; 16 bytes of the row per lane, which covers a row of up to
+// 128 elements) takes kPrepassRows query rows of one head, their loads all issued before the sums:
+// D = sum_d dO*O, stored as k1 = -D, and nlc = -L*log2(e).
 // Block 0 also clears the status word, so every operator call starts clean.
+constexpr int kPrepassRows = 4;
 template <typename T>
 __global__ void prepass_kernel(const T* __restrict__ o, const T* __restrict__ d_o, const float* __restrict__ lse,
-                               float* __restrict__ nlc, float* __restrict__ k1, int* status, long rows, int d,
+                               float* __restrict__ nlc, float* __restrict__ k1, int* status, unsigned blocks_per_head, int d,
                                int n_q, int first_live_query, View vo, View vdo, long long lse_head,
-                               long long lse_batch) {
+                               long long lse_batch, int lanes) {
   if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
-  long row = static_cast<long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  int lane = threadIdx.x & 31;
+  // blocks do not straddle heads: head and row come from 32-bit arithmetic that is uniform per block
+  const int groups = blockDim.x / lanes;
+  const unsigned bh = blockIdx.x / blocks_per_head;
+  const int q0 = static_cast<int>(blockIdx.x - bh * blocks_per_head) * groups * kPrepassRows + static_cast<int>(threadIdx.x) / lanes;
+  constexpr int V = 16 / sizeof(T);
+  const int c = (threadIdx.x & (lanes - 1)) * V;
   // the inputs may be views (strides per row / head / batch entry), the row vectors are padded per head
-  const long bh = row / n_q, qi = row - bh * n_q;
-  const long vrow = bh * row_stride(n_q) + qi;
-  const long hb = bh / vo.heads, hh = bh - hb * vo.heads;
-  const float lse_row = lse[hb * lse_batch + hh * lse_head + qi];
-  if (row % n_q < first_live_query) {
-    // a query the causal mask leaves without any visible key (n_k < n_q): every P of its row is
-    // masked to zero in the passes, so the row contributes nothing and its dQ2 and ddO are zero.
-    // Its saved L (-inf) and O (0 or NaN, depending on who produced them) are not looked at.
-    if (lane == 0) {
-      nlc[vrow] = 0.f;
-      k1[vrow] = 0.f;
-    }
-    return;
-  }
-  if (o == nullptr) {
-    // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
-    if (lane == 0) nlc[vrow] = -lse_row * kLog2e;
-    return;
-  }
-  const T* po = o + hb * vo.batch + hh * vo.head + qi * vo.row;
-  const T* pd = d_o + hb * vdo.batch + hh * vdo.head + qi * vdo.row;
-  float acc = 0.f;
-  for (int c = lane; c < d; c += 32) acc = fmaf(static_cast<float>(po[c]), static_cast<float>(pd[c]), acc);
+  const unsigned hb = bh / static_cast<unsigned>(vo.heads), hh = bh - hb * static_cast<unsigned>(vo.heads);
+  const T* po = o + static_cast<long long>(hb) * vo.batch + static_cast<long long>(hh) * vo.head + c;
+  const T* pd = d_o + static_cast<long long>(hb) * vdo.batch + static_cast<long long>(hh) * vdo.head + c;
+  // a query the causal mask leaves without any visible key (n_k < n_q): every P of its row is
+  // masked to zero in the passes, so the row contributes nothing and its dQ2 and ddO are zero.
+  // Its saved L (-inf) and O (0 or NaN, depending on who produced them) are not looked at.
+  uint4 a[kPrepassRows], b[kPrepassRows];
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
-    k1[vrow] = -acc;
-    nlc[vrow] = -lse_row * kLog2e;
+  for (int r = 0; r < kPrepassRows; ++r) {
+    const int qi = q0 + r * groups;
+    a[r] = b[r] = make_uint4(0u, 0u, 0u, 0u);
+    if (o != nullptr && c < d && qi < n_q && qi >= first_live_query) {
+      a[r] = *reinterpret_cast<const uint4*>(po + qi * vo.row);
+      b[r] = *reinterpret_cast<const uint4*>(pd + qi * vdo.row);
+    }
+  }
+  float* nlc_head = nlc + static_cast<long>(bh) * row_stride(n_q);
+  float* k1_head = k1 + static_cast<long>(bh) * row_stride(n_q);
+  const float* lse_h = lse + static_cast<long long>(hb) * lse_batch + static_cast<long long>(hh) * lse_head;
+#pragma unroll
+  for (int r = 0; r < kPrepassRows; ++r) {
+    const int qi = q0 + r * groups;
+    const T* ea = reinterpret_cast<const T*>(&a[r]);
+    const T* eb = reinterpret_cast<const T*>(&b[r]);
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc = fmaf(static_cast<float>(ea[e]), static_cast<float>(eb[e]), acc);
+    for (int off = lanes >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (c != 0 || qi >= n_q) continue;
+    if (qi < first_live_query) {
+      nlc_head[qi] = 0.f;
+      k1_head[qi] = 0.f;
+      continue;
+    }
+    nlc_head[qi] = -lse_h[qi] * kLog2e;
+    // no O: D comes out of the sweep that yields dd and b (sum_j P dP), which then writes k1
+    if (o != nullptr) k1_head[qi] = -acc;
   }
 }
 
@@ -221,27 +236,33 @@ static int run_prepass(const FhobProblem* p, void* stream, bool for_operator = t
     if (st != FHOB_OK) return st;
   }
   RowVectors rv = row_vectors(*p);
-  long rows = static_cast<long>(p->bh) * p->n_q;
-  const int warps = 8;
-  unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  const int dv_ = head_dim_v(*p);
+  // lanes per row: enough 16-byte pieces to cover a row in one step, at most a warp
+  const int pieces = dv_ * (p->dtype == FHOB_F32 ? 4 : 2) / 16;
+  int lanes = 1;
+  while (lanes < pieces && lanes < 32) lanes <<= 1;
+  const int threads = 256, per_block = threads / lanes * kPrepassRows;
+  const unsigned blocks_per_head = static_cast<unsigned>((p->n_q + per_block - 1) / per_block);
+  const unsigned long long blocks = static_cast<unsigned long long>(blocks_per_head) * static_cast<unsigned>(p->bh);
+  if (blocks > 0x7fffffffull) return FHOB_ERR_SHAPE;
+  const unsigned grid = static_cast<unsigned>(blocks);
   // bottom-right aligned causal mask: query i sees key 0 only if i + n_k - n_q >= 0
   const int first_live = (p->causal && p->n_q > p->n_k) ? p->n_q - p->n_k : 0;
-  const int dv_ = head_dim_v(*p);
   const View vo = tensor_view(*p, kTenO, p->n_q, dv_), vdo = tensor_view(*p, kTenDO, p->n_q, dv_);
   const long long lse_head = p->layout ? p->layout->lse_head : p->n_q;
   const long long lse_batch = p->layout ? p->layout->lse_batch : static_cast<long long>(p->bh) * p->n_q;
   if (p->dtype == FHOB_BF16) {
-    prepass_kernel<__nv_bfloat16><<<grid, warps * 32, 0, s>>>(
+    prepass_kernel<__nv_bfloat16><<<grid, threads, 0, s>>>(
         static_cast<const __nv_bfloat16*>(p->o), static_cast<const __nv_bfloat16*>(p->d_o), p->lse, rv.nlc, rv.k1,
-        rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
+        rv.status, blocks_per_head, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch, lanes);
   } else if (p->dtype == FHOB_F16) {
-    prepass_kernel<__half><<<grid, warps * 32, 0, s>>>(static_cast<const __half*>(p->o),
+    prepass_kernel<__half><<<grid, threads, 0, s>>>(static_cast<const __half*>(p->o),
                                                        static_cast<const __half*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                       rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
+                                                       rv.status, blocks_per_head, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch, lanes);
   } else {
-    prepass_kernel<float><<<grid, warps * 32, 0, s>>>(static_cast<const float*>(p->o),
+    prepass_kernel<float><<<grid, threads, 0, s>>>(static_cast<const float*>(p->o),
                                                       static_cast<const float*>(p->d_o), p->lse, rv.nlc, rv.k1,
-                                                      rv.status, rows, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch);
+                                                      rv.status, blocks_per_head, dv_, p->n_q, first_live, vo, vdo, lse_head, lse_batch, lanes);
   }
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
