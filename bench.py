@@ -686,6 +686,21 @@ def main():
             torch.cuda.synchronize()
             nbytes = (big if name == "h2d" else x["k"]).numel() * 2
             link[name] = nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+        # and with both directions busy in the step's own proportion (two parts up, one part down),
+        # which is what the pipelined path asks of the link
+        up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        up.wait_stream(torch.cuda.current_stream(dev))
+        down.wait_stream(torch.cuda.current_stream(dev))
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(up):
+            u0.record()
+            for _ in range(2):
+                dst.copy_(big, non_blocking=True)
+            u1.record()
+        with torch.cuda.stream(down):
+            host_out[1].copy_(x["k"], non_blocking=True)
+        torch.cuda.synchronize()
+        link["h2d_duplex"] = 2 * big.numel() * 2 / (u0.elapsed_time(u1) * 1e-3) / 1e9
         del dst
         def e2e_step():
             return fhob.flash_bwdbwd(*host, case.scale, is_causal=w["causal"], device=dev, out=host_out)
@@ -707,6 +722,8 @@ def main():
                    d2h_gbs=round(case.out_bytes / (ms_e2e * 1e-3) / 1e9, 1),
                    link_alone_h2d_gbs=round(link["h2d"], 1), link_alone_d2h_gbs=round(link["d2h"], 1),
                    frac_of_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d"], 3),
+                   link_duplex_h2d_gbs=round(link["h2d_duplex"], 1),
+                   frac_of_duplex_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d_duplex"], 3),
                    host_placement=placement)
         del host, host_out
 

@@ -281,7 +281,7 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
 
 
 _copy_streams: dict = {}
-HOST_RANGE_BYTES = 96 << 20   # input bytes staged per head range on the host-buffer path
+HOST_RANGE_BYTES = 192 << 20   # input bytes staged per head range on the host-buffer path (measured best of 48-768 MB)
 
 
 def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None, range_bytes=None):
