@@ -352,8 +352,8 @@ def test_config_causal_4096_d128():
 
 
 def test_config_long_context_32768_d128():
-    """One GPU's share (4 of 32 heads) of the long-context causal configuration."""
-    _large_case(4, 32768, 32768, 128, True, seed=1236, heads_checked=(3,))
+    """The long-context causal configuration at full size (B=1, H=32, N=32768, D=128)."""
+    _large_case(32, 32768, 32768, 128, True, seed=1236, heads_checked=(0, 31))
 
 
 def test_config_cross_attention_4096x8192_d128():
@@ -373,6 +373,27 @@ def test_config_cross_attention_4096x8192_d128():
     doubled = fhob.flash_bwdbwd(*args(slice(0, 2), 2.0), check=True)
     for a, b in zip(got, doubled):
         assert O.rel_err(b, 2.0 * a[0:2].float()) < 2e-2   # linear in the cotangents (powers of two: near exact)
+
+
+def test_full_cross_attention_job_512_heads():
+    """The whole cross-attention scaling job on one GPU (B=16, H=32 -> 512 heads, N_Q=4096, N_K=8192,
+    D=128; 6.4 GB of inputs): first and last head against the fp64 oracle, and properties that hold
+    bit for bit at any size - the operator is linear in (ddQ, ddK, ddV), doubling is exact in
+    floating point, and a head's result does not depend on which launch it is part of."""
+    import fhob
+    x, o, lse, got = _large_case(512, 4096, 8192, 128, False, seed=1240, heads_checked=(0, 511))
+    scale = 128 ** -0.5
+    doubled = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"] * 2, x["ddk"] * 2, x["ddv"] * 2, lse,
+                                scale, check=True)
+    for n, a, b in zip(OUT_NAMES, got, doubled):
+        assert torch.equal(b, a * 2), n
+    del doubled
+    for h in (0, 255, 511):
+        s = slice(h, h + 1)
+        alone = fhob.flash_bwdbwd(x["q"][s], x["k"][s], x["v"][s], o[s], x["do"][s], x["ddq"][s], x["ddk"][s],
+                                  x["ddv"][s], lse[s], scale, check=True)
+        for n, a, b in zip(OUT_NAMES, got, alone):
+            assert torch.equal(a[s], b), (n, h)
 
 
 def test_memory_is_linear_in_sequence_length():
