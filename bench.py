@@ -65,11 +65,12 @@ EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass at N_Q=4096,
 # N_K=8192, D=128, from an ncu capture of a 16-head case (every head has its own tensors, so the
 # traffic of a launch grows in proportion to its heads).
-DRAM_BYTES_PER_HEAD = {("cfg5", "pass12"): 191.70e6 / 16, ("cfg5", "pass3"): 211.38e6 / 16,
-                       ("cfg5", "pass4"): 230.23e6 / 16}
-# template arguments: pass, head dim of q/k, head dim of v, streamed rows, fused dd+b sweep, fp16 storage
-KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, {d}, 64, 1, 0>",
-                "pass3": "tc_pass_kernel<3, {d}, {d}, 64, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, {d}, 64, 0, 0>"}
+DRAM_BYTES_PER_HEAD = {("cfg5", "pass12"): 190.32e6 / 16, ("cfg5", "pass3"): 213.21e6 / 16,
+                       ("cfg5", "pass4"): 229.11e6 / 16}
+# template arguments: pass, head dim of q/k, head dim of v, streamed rows, fused dd+b sweep, fp16 storage,
+# split fp32 operands
+KERNEL_NAMES = {"pass12": "tc_pass_kernel<2, {d}, {d}, 64, 1, 0, 0>",
+                "pass3": "tc_pass_kernel<3, {d}, {d}, 64, 0, 0, 0>", "pass4": "tc_pass_kernel<4, {d}, {d}, 64, 0, 0, 0>"}
 METRIC = "double_backward_attention_tflops"
 
 _JSON_FD = None
