@@ -28,18 +28,20 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-def make_inputs(bh, nq, nk, d, seed, dtype=torch.float32, device="cpu", cot_scale=1.0):
+def make_inputs(bh, nq, nk, d, seed, dtype=torch.float32, device="cpu", cot_scale=1.0, on_device=False):
     """Seven seeded N(0,1) tensors with bf16-representable values.
 
     Layout (BH, N, D) like the reference entry point.  ``cot_scale`` scales dO
-    and the three cotangents (one benchmark configuration uses 0.1).
+    and the three cotangents (one benchmark configuration uses 0.1).  ``on_device``
+    draws the numbers with the device's generator (for the multi-gigabyte cases).
     """
-    g = torch.Generator().manual_seed(seed)
+    gen_dev = device if on_device else "cpu"
+    g = torch.Generator(device=gen_dev).manual_seed(seed)
     shapes = dict(q=(bh, nq, d), k=(bh, nk, d), v=(bh, nk, d), do=(bh, nq, d),
                   ddq=(bh, nq, d), ddk=(bh, nk, d), ddv=(bh, nk, d))
     out = {}
     for n, s in shapes.items():
-        t = torch.randn(s, generator=g, dtype=torch.float32)
+        t = torch.randn(s, generator=g, dtype=torch.float32, device=gen_dev)
         if n in ("do", "ddq", "ddk", "ddv"):
             t = t * cot_scale
         out[n] = t.bfloat16().to(dtype).to(device)

@@ -329,7 +329,8 @@ def test_forward_producer(causal):
 def _large_case(bh, nq, nk, d, causal, seed, cot_scale=1.0, heads_checked=(0,)):
     """Full-size run; the listed heads are checked against the chunked fp64 oracle on the GPU."""
     import fhob
-    x = make_inputs(bh, nq, nk, d, seed=seed, dtype=torch.bfloat16, device="cuda", cot_scale=cot_scale)
+    x = make_inputs(bh, nq, nk, d, seed=seed, dtype=torch.bfloat16, device="cuda", cot_scale=cot_scale,
+                    on_device=bh * max(nq, nk) * d > 1 << 28)
     scale = d ** -0.5
     o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], scale, is_causal=causal)
     got = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, scale,
@@ -394,6 +395,17 @@ def test_full_cross_attention_job_512_heads():
                                   x["ddv"][s], lse[s], scale, check=True)
         for n, a, b in zip(OUT_NAMES, got, alone):
             assert torch.equal(a[s], b), (n, h)
+
+
+@pytest.mark.parametrize("nq,nk", [(16384, 128), (128, 16384)])
+def test_tensors_with_more_than_2_to_31_elements(nq, nk):
+    """1025 heads x 16384 rows x 128 columns = 2.15e9 elements per tensor on one side: every offset
+    beyond the first 2^31 elements (4 GiB) has to be computed in 64 bits.  The last head is the one
+    that would show a wrapped offset."""
+    x, o, lse, got = _large_case(1025, nq, nk, 128, False, seed=1241, heads_checked=(0, 1024))
+    assert max(t.numel() for t in got) > 2 ** 31
+    del x, o, lse, got
+    torch.cuda.empty_cache()
 
 
 def test_memory_is_linear_in_sequence_length():
