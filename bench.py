@@ -687,6 +687,19 @@ def main():
             torch.cuda.synchronize()
             nbytes = (big if name == "h2d" else x["k"]).numel() * 2
             link[name] = nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9
+        # every input tensor alone: pinned buffers that landed on a remote memory node show up here
+        per_tensor = []
+        for t in host[:8]:
+            d_t = dst[: t.shape[0]] if t.shape == big.shape else torch.empty_like(t, device=dev)
+            d_t.copy_(t, non_blocking=True)
+            torch.cuda.synchronize()
+            e0.record()
+            d_t.copy_(t, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            per_tensor.append(round(t.numel() * t.element_size() / (e0.elapsed_time(e1) * 1e-3) / 1e9, 1))
+            del d_t
+        link["h2d_per_tensor"] = per_tensor
         # and with both directions busy in the step's own proportion (two parts up, one part down),
         # which is what the pipelined path asks of the link
         up, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
@@ -723,6 +736,7 @@ def main():
                    d2h_gbs=round(case.out_bytes / (ms_e2e * 1e-3) / 1e9, 1),
                    link_alone_h2d_gbs=round(link["h2d"], 1), link_alone_d2h_gbs=round(link["d2h"], 1),
                    frac_of_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d"], 3),
+                   link_alone_h2d_gbs_per_input=link["h2d_per_tensor"],
                    link_duplex_h2d_gbs=round(link["h2d_duplex"], 1),
                    frac_of_duplex_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d_duplex"], 3),
                    host_placement=placement)

@@ -281,6 +281,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
 
 
 _copy_streams: dict = {}
+_staging: dict = {}     # (device, heads per range, shapes) -> ring of device staging sets of the host-buffer path
+HOST_STAGES = 3
 HOST_RANGE_BYTES = 192 << 20   # input bytes staged per head range on the host-buffer path (measured best of 48-768 MB)
 
 
@@ -288,9 +290,9 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     """Host tensors in, pinned host tensors out.  Heads are independent, so the batch is cut into
     head ranges of about ``HOST_RANGE_BYTES`` of input each (at least four ranges when there are
     that many heads) that flow through three streams: upload of range i+1, the kernels of range i
-    and the download of range i-1 overlap.  Device staging memory comes from torch's caching
-    allocator, so after the first call of a shape nothing is allocated on the device, and the
-    results' pinned buffers come from torch's caching host allocator."""
+    and the download of range i-1 overlap.  Device staging memory is a ring of three sets of
+    buffers kept per device and shape, so after the first call of a shape nothing is allocated on
+    the device; the results' pinned buffers come from torch's caching host allocator (or ``out=``)."""
     names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
     out_shapes = (mats[0].shape, mats[1].shape, mats[2].shape, mats[4].shape)   # dQ2, dK2, dV2, ddO
     mats3 = [_fold(t, n) for t, n in zip(mats, names)]
@@ -316,32 +318,65 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     per_range = max(1, int(range_bytes or HOST_RANGE_BYTES) // max(1, head_bytes))
     n_chunks = max(-(-bh // per_range), min(bh, 4))
     bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
+    # what follows the last upload (its kernels and its download) is not overlapped with anything:
+    # the last range is cut into a half and two quarters so that this tail is short
+    lo_last, hi_last = bounds[-2], bounds[-1]
+    if n_chunks >= 4 and hi_last - lo_last >= 4:
+        q = (hi_last - lo_last) // 4
+        bounds[-1:] = [hi_last - 2 * q, hi_last - q, hi_last]
+        n_chunks += 2
     widest = max(hi - lo for lo, hi in zip(bounds, bounds[1:]))
     sizing = _lib.FhobProblem()       # the widest range decides the workspace (fp32: room for the bf16 copies too)
     sizing.bh, sizing.n_q, sizing.n_k, sizing.d = widest, mats3[0].shape[1], mats3[1].shape[1], mats3[0].shape[2]
     sizing.d_v = 0 if mats3[2].shape[2] == mats3[0].shape[2] else mats3[2].shape[2]
     sizing.dtype, sizing.impl = _lib.DTYPES[str(mats3[0].dtype)], _lib.IMPL[impl]
     ws = _workspace(dev, main.cuda_stream, _lib.load().fhob_workspace_bytes_problem(C.byref(sizing)))
+    # Device staging: a ring of HOST_STAGES sets of buffers (nine inputs and four results of the widest
+    # range), kept per device and shape, so that a call allocates nothing on the device and the
+    # pipeline's timing does not depend on the state of the caching allocator.  Set s is reused by
+    # range i + HOST_STAGES once the kernels that read its inputs and the download of its results are done.
+    key = (dev.index, widest, tuple((tuple(t.shape[1:]), t.dtype) for t in mats3))
+    ring = _staging.get(key)
+    if ring is None:
+        if len(_staging) >= 4:
+            _staging.clear()
+        ring = []
+        for _ in range(min(HOST_STAGES, n_chunks)):
+            ins = [torch.empty((widest,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in mats3]
+            ins.append(torch.empty((widest, lse.shape[1]), dtype=torch.float32, device=dev))
+            res = [torch.empty((widest,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in want]
+            ring.append(dict(ins=ins, res=res, read=None, drained=None))
+        _staging[key] = ring
+    for st in ring:
+        # a previous call may still be using the set on other streams
+        st["read"] = st["drained"] = None
+    up.wait_stream(down)
     # the pre-pass of every range clears the status word, so each range's word is kept
     status_host = torch.zeros(n_chunks, dtype=torch.int32, pin_memory=True) if check else None
     for i, (lo, hi) in enumerate(zip(bounds, bounds[1:])):
+        st, n = ring[i % len(ring)], hi - lo
         with torch.cuda.stream(up):
-            staged = [t[lo:hi].to(dev, non_blocking=True) for t in mats3 + [lse]]
+            if st["read"] is not None:
+                up.wait_event(st["read"])
+            for src, dst in zip(mats3 + [lse], st["ins"]):
+                dst[:n].copy_(src[lo:hi], non_blocking=True)
             ready = torch.cuda.Event()
             ready.record(up)
         main.wait_event(ready)
-        for t in staged:
-            t.record_stream(main)
-        res = _run_device(*staged, scale, is_causal, impl, False, window, workspace=ws)
+        if st["drained"] is not None:
+            main.wait_event(st["drained"])
+        res = _run_device(*(t[:n] for t in st["ins"]), scale, is_causal, impl, False, window,
+                          out=tuple(t[:n] for t in st["res"]), workspace=ws)
         if check:
             status_host[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
-        done = torch.cuda.Event()
-        done.record(main)
-        down.wait_event(done)
+        st["read"] = torch.cuda.Event()
+        st["read"].record(main)
+        down.wait_event(st["read"])
         with torch.cuda.stream(down):
             for h, r in zip(outs_host, res):
-                r.record_stream(down)
                 h[lo:hi].copy_(r.reshape(h[lo:hi].shape), non_blocking=True)
+            st["drained"] = torch.cuda.Event()
+            st["drained"].record(down)
     down.synchronize()
     if check:
         main.synchronize()
