@@ -30,9 +30,15 @@ struct SimtParams {
   void *dq2, *dk2, *dv2, *ddo;
   const float *nlc, *k1;
   float *ndd, *k23;
-  int n_q, n_k, d, dv, causal, window;
+  int bh, n_q, n_k, d, dv, causal, window;
   float scale;
 };
+
+// Grid of (stationary tiles, heads): heads beyond what grid.y can index continue in grid.z.
+constexpr int kMaxGridY = 65535;
+inline dim3 head_grid(int tiles, int bh) {
+  return dim3(tiles, bh < kMaxGridY ? bh : kMaxGridY, (bh + kMaxGridY - 1) / kMaxGridY);
+}
 
 template <typename T>
 __device__ __forceinline__ float ld_elem(const void* p, size_t i);
@@ -104,7 +110,8 @@ __global__ void __launch_bounds__(NT) simt_pass_kernel(const SimtParams p) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * TM;
-  const int bh = blockIdx.y;
+  const int bh = blockIdx.y + blockIdx.z * kMaxGridY;   // see head_grid
+  if (bh >= p.bh) return;
   const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
   const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);  // row-vector offset
@@ -305,7 +312,8 @@ __global__ void __launch_bounds__(NT) simt_forward_kernel(const SimtParams p, vo
   float* ps = vs + TN * ld;  // [TM][TN+1]
   constexpr int LT = TN + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TM, bh = blockIdx.y;
+  const int m0 = blockIdx.x * TM, bh = blockIdx.y + blockIdx.z * kMaxGridY;   // see head_grid
+  if (bh >= p.bh) return;
   const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
   const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const int causal_off = p.n_k - p.n_q;
@@ -397,7 +405,8 @@ __global__ void __launch_bounds__(NT) simt_backward_kernel(const SimtParams p, v
   float* svec = pt + 2 * TM * (TN + 1);      // [2][TN]: nlc, k1 of streamed queries (KSIDE)
   constexpr int LT = TN + 1;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * TM, bh = blockIdx.y;
+  const int m0 = blockIdx.x * TM, bh = blockIdx.y + blockIdx.z * kMaxGridY;   // see head_grid
+  if (bh >= p.bh) return;
   const size_t qoff = static_cast<size_t>(bh) * p.n_q * d, qoff_v = static_cast<size_t>(bh) * p.n_q * dv;
   const size_t koff = static_cast<size_t>(bh) * p.n_k * d, koff_v = static_cast<size_t>(bh) * p.n_k * dv;
   const size_t voff = static_cast<size_t>(bh) * row_stride(p.n_q);
@@ -517,7 +526,7 @@ SimtParams make_params(const FhobProblem& p) {
   s.q = p.q; s.k = p.k; s.v = p.v; s.d_o = p.d_o; s.ddq = p.ddq; s.ddk = p.ddk; s.ddv = p.ddv;
   s.dq2 = p.dq2; s.dk2 = p.dk2; s.dv2 = p.dv2; s.ddo = p.ddo;
   s.nlc = rv.nlc; s.k1 = rv.k1; s.ndd = rv.ndd; s.k23 = rv.k23;
-  s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.dv = head_dim_v(p); s.causal = p.causal; s.window = p.window; s.scale = p.scale;
+  s.bh = p.bh; s.n_q = p.n_q; s.n_k = p.n_k; s.d = p.d; s.dv = head_dim_v(p); s.causal = p.causal; s.window = p.window; s.scale = p.scale;
   return s;
 }
 
@@ -527,7 +536,7 @@ int launch_pass(const FhobProblem& p, cudaStream_t st) {
   FHOB_CUDA_OK(cudaFuncSetAttribute(simt_pass_kernel<T, PASS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem)));
   int n_stat = PASS == 4 ? p.n_k : p.n_q;
-  dim3 grid((n_stat + TM - 1) / TM, p.bh);
+  dim3 grid = head_grid((n_stat + TM - 1) / TM, p.bh);
   simt_pass_kernel<T, PASS><<<grid, NT, smem, st>>>(make_params(p));
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
@@ -552,9 +561,9 @@ int launch_backward(const FhobProblem& p, void* dq, void* dk, void* dv, cudaStre
                                     static_cast<int>(smem)));
   FHOB_CUDA_OK(cudaFuncSetAttribute(simt_backward_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     static_cast<int>(smem)));
-  simt_backward_kernel<T, false><<<dim3((p.n_q + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dq, nullptr);
+  simt_backward_kernel<T, false><<<head_grid((p.n_q + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dq, nullptr);
   FHOB_CUDA_OK(cudaGetLastError());
-  simt_backward_kernel<T, true><<<dim3((p.n_k + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dk, dv);
+  simt_backward_kernel<T, true><<<head_grid((p.n_k + TM - 1) / TM, p.bh), NT, smem, st>>>(s, dk, dv);
   FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
 }
@@ -578,7 +587,7 @@ int simt_pass(int pass, const FhobProblem& p, cudaStream_t st) {
 int simt_forward(const FhobProblem& p, void* o_out, float* lse_out, cudaStream_t st) {
   if (p.d > 32 * DCH || head_dim_v(p) > 32 * DCH) return FHOB_ERR_SHAPE;
   size_t smem = sizeof(float) * ((TM + 2 * TN) * pitch(p) + TM * (TN + 1));
-  dim3 grid((p.n_q + TM - 1) / TM, p.bh);
+  dim3 grid = head_grid((p.n_q + TM - 1) / TM, p.bh);
   SimtParams s = make_params(p);
   if (p.dtype == FHOB_F32) {
     FHOB_CUDA_OK(cudaFuncSetAttribute(simt_forward_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,

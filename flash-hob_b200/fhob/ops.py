@@ -273,8 +273,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
                            out, workspace)
     if not torch.cuda.is_available():
         raise RuntimeError("flash_bwdbwd needs a CUDA device; there is no CPU implementation")
-    if O is None or workspace is not None:
-        raise ValueError("O=None and workspace= are only supported for device tensors")
+    if workspace is not None:
+        raise ValueError("workspace= is only supported for device tensors")
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     return _run_host((Q, K, V, O, dO, ddQ, ddK, ddV), L, scale, is_causal, impl, check is None or bool(check), dev,
                      window=sliding_window, out=out)
@@ -295,7 +295,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     the device; the results' pinned buffers come from torch's caching host allocator (or ``out=``)."""
     names = ("Q", "K", "V", "O", "dO", "ddQ", "ddK", "ddV")
     out_shapes = (mats[0].shape, mats[1].shape, mats[2].shape, mats[4].shape)   # dQ2, dK2, dV2, ddO
-    mats3 = [_fold(t, n) for t, n in zip(mats, names)]
+    mats3 = [None if t is None else _fold(t, n) for t, n in zip(mats, names)]   # O may be None (not uploaded then)
     bh = mats3[0].shape[0]
     lse = (L.reshape(-1, L.shape[-1]) if L.dim() >= 2 else L.reshape(1, -1)).to(torch.float32)
     if lse.shape[0] != bh:
@@ -314,7 +314,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     main = torch.cuda.current_stream(dev)
     up, down = _copy_streams.setdefault(dev.index, (torch.cuda.Stream(dev), torch.cuda.Stream(dev)))
     up.wait_stream(main)
-    head_bytes = sum(t[0].numel() * t.element_size() for t in mats3) + lse[0].numel() * 4
+    head_bytes = sum(t[0].numel() * t.element_size() for t in mats3 if t is not None) + lse[0].numel() * 4
     per_range = max(1, int(range_bytes or HOST_RANGE_BYTES) // max(1, head_bytes))
     n_chunks = max(-(-bh // per_range), min(bh, 4))
     bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
@@ -335,14 +335,15 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     # range), kept per device and shape, so that a call allocates nothing on the device and the
     # pipeline's timing does not depend on the state of the caching allocator.  Set s is reused by
     # range i + HOST_STAGES once the kernels that read its inputs and the download of its results are done.
-    key = (dev.index, widest, tuple((tuple(t.shape[1:]), t.dtype) for t in mats3))
+    key = (dev.index, widest, tuple(None if t is None else (tuple(t.shape[1:]), t.dtype) for t in mats3))
     ring = _staging.get(key)
     if ring is None:
         if len(_staging) >= 4:
             _staging.clear()
         ring = []
         for _ in range(min(HOST_STAGES, n_chunks)):
-            ins = [torch.empty((widest,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in mats3]
+            ins = [None if t is None else torch.empty((widest,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev)
+                   for t in mats3]
             ins.append(torch.empty((widest, lse.shape[1]), dtype=torch.float32, device=dev))
             res = [torch.empty((widest,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in want]
             ring.append(dict(ins=ins, res=res, read=None, drained=None))
@@ -359,13 +360,14 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
             if st["read"] is not None:
                 up.wait_event(st["read"])
             for src, dst in zip(mats3 + [lse], st["ins"]):
-                dst[:n].copy_(src[lo:hi], non_blocking=True)
+                if src is not None:
+                    dst[:n].copy_(src[lo:hi], non_blocking=True)
             ready = torch.cuda.Event()
             ready.record(up)
         main.wait_event(ready)
         if st["drained"] is not None:
             main.wait_event(st["drained"])
-        res = _run_device(*(t[:n] for t in st["ins"]), scale, is_causal, impl, False, window,
+        res = _run_device(*(None if t is None else t[:n] for t in st["ins"]), scale, is_causal, impl, False, window,
                           out=tuple(t[:n] for t in st["res"]), workspace=ws)
         if check:
             status_host[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
@@ -383,6 +385,15 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
         for status in status_host.tolist():
             _lib.check(status, "fhob_bwdbwd (device status)")
     return tuple(t.reshape(s) for t, s in zip(outs_host, out_shapes))
+
+
+def release_cached_memory() -> None:
+    """Drops the per-stream workspaces and the staging sets of the host-buffer path (device memory
+    this module keeps between calls so that repeated calls allocate nothing).  Call it with no
+    operator call in flight."""
+    torch.cuda.synchronize()
+    _workspaces.clear()
+    _staging.clear()
 
 
 def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_window: Optional[int] = None,

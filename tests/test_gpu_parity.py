@@ -408,6 +408,23 @@ def test_tensors_with_more_than_2_to_31_elements(nq, nk):
     torch.cuda.empty_cache()
 
 
+@pytest.mark.parametrize("impl,dtype,tol", [("simt", torch.float32, TOL_F32), ("tcgen05", torch.bfloat16, TOL_BF16)])
+def test_more_heads_than_one_grid_dimension_indexes(impl, dtype, tol):
+    """70 000 heads of a tiny problem: the head index does not fit the y dimension of a launch grid."""
+    import fhob
+    bh = 70000
+    x = make_inputs(bh, 40, 56, 16, seed=1242, dtype=dtype, device="cuda", on_device=True)
+    o, lse = fhob.attention_forward(x["q"], x["k"], x["v"], 0.25, is_causal=True, impl=impl)
+    got = fhob.flash_bwdbwd(x["q"], x["k"], x["v"], o, x["do"], x["ddq"], x["ddk"], x["ddv"], lse, 0.25,
+                            is_causal=True, impl=impl, check=True)
+    for h in (0, 65534, 65535, 65536, bh - 1):
+        one = {n: t[h:h + 1].double().cpu() for n, t in x.items()}
+        ref, lse_ref, _, _ = _oracle(one, 0.25, True)
+        assert O.rel_err(lse[h:h + 1].cpu(), lse_ref) < 1e-4
+        for n, g, r in zip(OUT_NAMES, got, ref):
+            assert O.rel_err(g[h:h + 1].cpu(), r) < tol, (n, h)
+
+
 def test_memory_is_linear_in_sequence_length():
     import fhob
     peaks = []
@@ -437,6 +454,30 @@ def test_host_buffers_end_to_end():
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert g.device.type == "cpu"
         assert O.rel_err(g, r) < TOL_BF16, n
+    # many ranges (one head each), more than the ring of staging sets holds, into caller-owned tensors, twice
+    x = make_inputs(9, 192, 320, 64, seed=82, dtype=torch.float64)
+    ref, lse, o, _ = _oracle(x, 0.125, True)
+    host = {k: v.bfloat16().pin_memory() for k, v in x.items()}
+    outs = tuple(torch.empty(t.shape, dtype=torch.bfloat16).pin_memory() for t in (x["q"], x["k"], x["k"], x["q"]))
+    saved = fhob.ops.HOST_RANGE_BYTES
+    try:
+        fhob.ops.HOST_RANGE_BYTES = 1      # one head per range
+        for _ in range(2):
+            for t in outs:
+                t.zero_()
+            got = fhob.flash_bwdbwd(host["q"], host["k"], host["v"], o.bfloat16().pin_memory(), host["do"],
+                                    host["ddq"], host["ddk"], host["ddv"], lse.float().pin_memory(), 0.125,
+                                    is_causal=True, out=outs)
+            for n, g, t, r in zip(OUT_NAMES, got, outs, ref):
+                assert g.data_ptr() == t.data_ptr()
+                assert O.rel_err(g, r) < TOL_BF16, n
+        # without the saved forward output: it is not uploaded at all
+        got = fhob.flash_bwdbwd(host["q"], host["k"], host["v"], None, host["do"], host["ddq"], host["ddk"],
+                                host["ddv"], lse.float().pin_memory(), 0.125, is_causal=True)
+        for n, g, r in zip(OUT_NAMES, got, ref):
+            assert O.rel_err(g, r) < TOL_BF16, n
+    finally:
+        fhob.ops.HOST_RANGE_BYTES = saved
 
 
 def test_wrong_inputs_raise():
