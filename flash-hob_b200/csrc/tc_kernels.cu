@@ -862,18 +862,29 @@ __global__ void __launch_bounds__(NTHREADS, 1) tc_pass_kernel(const __grid_const
 // ------------------------------------------------------------------ host side
 
 // fp32 rows of d <= 64 columns -> [hi(64) | lo(64)] bf16 rows (see split_pack), zero beyond d: one
-// thread per pair of columns of the 64-wide row.
-__global__ void split_rows_kernel(const float* __restrict__ src, uint32_t* __restrict__ dst, long pairs, int d,
-                                  int n_rows, View v) {
+// thread per pair of columns of the 64-wide row.  One launch converts all the tensors a call needs
+// (blockIdx.y = tensor), which matters for the small problems whose time is mostly launches.
+struct SplitJobs {
+  const float* src[7];
+  uint32_t* dst[7];
+  long pairs[7];
+  int d[7], n_rows[7];
+  View view[7];
+};
+__global__ void split_rows_kernel(const __grid_constant__ SplitJobs jobs) {
+  const int t = blockIdx.y;
   const long i = static_cast<long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (i >= pairs) return;
+  if (i >= jobs.pairs[t]) return;
+  const int d = jobs.d[t], n_rows = jobs.n_rows[t];
+  const View& v = jobs.view[t];
   const long row = i >> 5;          // 32 pairs of columns per row of 64; rows of the copy are dense (bh, n, 128)
   const int c2 = static_cast<int>(i & 31);
   const long bh = row / n_rows, r = row - bh * n_rows;
-  const float* s = src + (bh / v.heads) * v.batch + (bh % v.heads) * v.head + r * v.row;   // the source may be a view
+  const float* s = jobs.src[t] + (bh / v.heads) * v.batch + (bh % v.heads) * v.head + r * v.row;   // the source may be a view
   const float2 x = 2 * c2 < d ? *reinterpret_cast<const float2*>(s + 2 * c2) : make_float2(0.f, 0.f);
   uint32_t hi, lo;
   split_pack(x.x, x.y, hi, lo);
+  uint32_t* dst = jobs.dst[t];
   dst[row * 64 + c2] = hi;          // a split row is 128 bf16 = 64 words: hi in words [0, 32), lo in [32, 64)
   dst[row * 64 + 32 + c2] = lo;
 }
@@ -995,18 +1006,33 @@ int tc_split_inputs(const FhobProblem& p, cudaStream_t s, int which) {
   const void* src[7] = {p.q, p.ddq, p.d_o, p.k, p.ddk, p.v, p.ddv};   // bit i of `which` = tensor i
   const int ids[7] = {kTenQ, kTenDDQ, kTenDO, kTenK, kTenDDK, kTenV, kTenDDV};
   void* dst[7] = {sb.q, sb.ddq, sb.d_o, sb.k, sb.ddk, sb.v, sb.ddv};
+  SplitJobs jobs;
+  int count = 0;
+  long most = 0;
   for (int i = 0; i < 7; ++i) {
     if (!(which & (1 << i))) continue;
     if (!src[i]) return FHOB_ERR_ARG;
     const int n_rows = i < 3 ? p.n_q : p.n_k;
-    const long pairs = static_cast<long>(p.bh) * n_rows * 32;
     const bool v_side = i == 2 || i >= 5;   // dO, V, ddV
     const int d = v_side ? head_dim_v(p) : p.d;
-    split_rows_kernel<<<static_cast<unsigned>((pairs + 255) / 256), 256, 0, s>>>(
-        static_cast<const float*>(src[i]), static_cast<uint32_t*>(dst[i]), pairs, d, n_rows,
-        tensor_view(p, ids[i], n_rows, d));
-    FHOB_CUDA_OK(cudaGetLastError());
+    jobs.src[count] = static_cast<const float*>(src[i]);
+    jobs.dst[count] = static_cast<uint32_t*>(dst[i]);
+    jobs.pairs[count] = static_cast<long>(p.bh) * n_rows * 32;
+    jobs.d[count] = d;
+    jobs.n_rows[count] = n_rows;
+    jobs.view[count] = tensor_view(p, ids[i], n_rows, d);
+    most = jobs.pairs[count] > most ? jobs.pairs[count] : most;
+    ++count;
   }
+  if (count == 0) return FHOB_OK;
+  for (int i = count; i < 7; ++i) {   // unused entries: defined, never read
+    jobs.src[i] = nullptr; jobs.dst[i] = nullptr; jobs.pairs[i] = 0; jobs.d[i] = 0; jobs.n_rows[i] = 1;
+    jobs.view[i] = jobs.view[0];
+  }
+  const long blocks = (most + 255) / 256;
+  if (blocks > 0x7fffffffL) return FHOB_ERR_SHAPE;
+  split_rows_kernel<<<dim3(static_cast<unsigned>(blocks), count), 256, 0, s>>>(jobs);
+  FHOB_CUDA_OK(cudaGetLastError());
   return FHOB_OK;
 }
 
