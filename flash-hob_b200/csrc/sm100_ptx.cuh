@@ -21,9 +21,6 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 __device__ __forceinline__ void fence_barrier_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -47,17 +44,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
-// 3-D tiled load (x = innermost element coordinate, y = row, z = head) into shared memory;
-// completion is signalled on `bar` as transaction bytes.  x*elem_size must be a multiple of 16.
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-      : "memory");
-}
-
 // 4-D tiled load (x = innermost element coordinate, y = row, z = head within a batch entry, w = batch
-// entry); same completion mechanism and the same 16-byte rule for x.
+// entry) into shared memory; completion is signalled on `bar` as transaction bytes.  x*elem_size
+// must be a multiple of 16.
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const void* tmap, uint64_t* bar, int x, int y, int z,
                                             int w) {
   asm volatile(
@@ -122,12 +111,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
-// Lane l of the warp writes 8 consecutive 32-bit columns of its TMEM lane.
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
-               "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-               : "memory");
-}
 
 // ---------------------------------------------------------------- UMMA
 // Shared-memory matrix descriptor for a 128-byte-swizzled bf16 tile whose rows
@@ -136,15 +119,10 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
 //   K-major use  (contraction runs along the 128-byte row):   sbo = 1024, lbo unused.
 //   MN-major use (contraction runs down the rows):            sbo = 1024 (next 8 rows),
 //                                                             lbo = distance to the next 64 columns.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);          // start address, bits [0,14)
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;     // leading byte offset, bits [16,30)
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;     // stride byte offset, bits [32,46)
-  d |= static_cast<uint64_t>(1) << 46;                              // descriptor version (sm_100)
-  d |= static_cast<uint64_t>(2) << 61;                              // layout type: SWIZZLE_128B
-  return d;
-}
+// The descriptor is used in two 32-bit halves (umma_desc_lo / umma_desc_hi_sw128 below): start
+// address in bits [0,14) and leading byte offset in bits [16,30) of the low word (both in units of
+// 16 bytes); stride byte offset in bits [32,46), descriptor version 1 (sm_100) at bit 46 and the
+// layout type SWIZZLE_128B = 2 at bits [61,64) of the high word.
 
 // Instruction descriptor, kind::f16: bf16 x bf16 (or f16 x f16) -> fp32, M x N tile.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major,
@@ -158,25 +136,7 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_m
          | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by one thread.
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]; A is 128 lanes x 8 columns of packed bf16 pairs per K=16 step.
-__device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                        uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// The same two instructions with the descriptors split into 32-bit halves.  The low word holds
+// tcgen05.mma with the shared-memory descriptors split into 32-bit halves.  The low word holds
 // the start address (and LBO), so stepping through a tile is one 32-bit add per operand; the
 // high word (SBO, version, swizzle mode) is a constant of the layout.
 __device__ __forceinline__ constexpr uint32_t umma_desc_hi_sw128(uint32_t sbo_bytes) {
@@ -211,10 +171,6 @@ __device__ __forceinline__ void umma_ts_split(uint32_t d_tmem, uint32_t a_tmem, 
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
-}
-
-__device__ __forceinline__ void prefetch_l1(const void* p) {
-  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
 // ---------------------------------------------------------------- math
