@@ -286,6 +286,21 @@ HOST_STAGES = 3
 HOST_RANGE_BYTES = 192 << 20   # input bytes staged per head range on the host-buffer path (measured best of 48-768 MB)
 
 
+def _host_ranges(bh: int, head_bytes: int, range_bytes: int):
+    """Boundaries of the head ranges of the host-buffer path: ranges of about ``range_bytes`` of
+    input, at least four when there are that many heads.  What follows the last upload (its kernels
+    and its download) is not overlapped with anything, so the last range is cut into a half and
+    two quarters to keep that tail short."""
+    per_range = max(1, range_bytes // max(1, head_bytes))
+    n_chunks = max(-(-bh // per_range), min(bh, 4))
+    bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
+    lo_last, hi_last = bounds[-2], bounds[-1]
+    if n_chunks >= 4 and hi_last - lo_last >= 4:
+        q = (hi_last - lo_last) // 4
+        bounds[-1:] = [hi_last - 2 * q, hi_last - q, hi_last]
+    return bounds
+
+
 def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None, range_bytes=None):
     """Host tensors in, pinned host tensors out.  Heads are independent, so the batch is cut into
     head ranges of about ``HOST_RANGE_BYTES`` of input each (at least four ranges when there are
@@ -315,16 +330,8 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     up, down = _copy_streams.setdefault(dev.index, (torch.cuda.Stream(dev), torch.cuda.Stream(dev)))
     up.wait_stream(main)
     head_bytes = sum(t[0].numel() * t.element_size() for t in mats3 if t is not None) + lse[0].numel() * 4
-    per_range = max(1, int(range_bytes or HOST_RANGE_BYTES) // max(1, head_bytes))
-    n_chunks = max(-(-bh // per_range), min(bh, 4))
-    bounds = [(bh * i) // n_chunks for i in range(n_chunks + 1)]
-    # what follows the last upload (its kernels and its download) is not overlapped with anything:
-    # the last range is cut into a half and two quarters so that this tail is short
-    lo_last, hi_last = bounds[-2], bounds[-1]
-    if n_chunks >= 4 and hi_last - lo_last >= 4:
-        q = (hi_last - lo_last) // 4
-        bounds[-1:] = [hi_last - 2 * q, hi_last - q, hi_last]
-        n_chunks += 2
+    bounds = _host_ranges(bh, head_bytes, int(range_bytes or HOST_RANGE_BYTES))
+    n_chunks = len(bounds) - 1
     widest = max(hi - lo for lo, hi in zip(bounds, bounds[1:]))
     sizing = _lib.FhobProblem()       # the widest range decides the workspace (fp32: room for the bf16 copies too)
     sizing.bh, sizing.n_q, sizing.n_k, sizing.d = widest, mats3[0].shape[1], mats3[1].shape[1], mats3[0].shape[2]

@@ -54,3 +54,25 @@ def test_binding_is_a_no_op_without_topology(monkeypatch):
     with hostmem.near_device(0) as rec:
         assert rec == dict(bound=False)
         assert os.sched_getaffinity(0) == before
+
+
+def test_head_ranges_of_the_host_buffer_path():
+    """Ranges cover every head once, in order; there are at least four when there are that many
+    heads; no range is larger than the requested bytes allow (one head at least); and the last
+    range is cut into a half and two quarters so that the un-overlapped tail is short."""
+    from fhob import ops
+    for bh in (1, 2, 3, 4, 5, 7, 16, 63, 64, 512, 1025):
+        for head_bytes, range_bytes in ((1 << 20, 192 << 20), (12 << 20, 192 << 20), (300 << 20, 192 << 20), (1, 1)):
+            b = ops._host_ranges(bh, head_bytes, range_bytes)
+            assert b[0] == 0 and b[-1] == bh
+            sizes = [hi - lo for lo, hi in zip(b, b[1:])]
+            assert all(s > 0 for s in sizes), (bh, head_bytes, sizes)
+            assert len(sizes) >= min(bh, 4)
+            per_range = max(1, range_bytes // head_bytes)
+            assert max(sizes) <= per_range + 1           # even split of bh over ceil(bh / per_range) ranges
+            if len(sizes) >= 6 and sizes[0] >= 4:
+                assert sizes[-1] <= sizes[0] // 4 + 1 and sizes[-2] <= sizes[0] // 4 + 1
+    # the 512-head cross-attention job: 12.6 MB of input per head -> 15 heads per range
+    b = ops._host_ranges(512, 12599296, 192 << 20)
+    sizes = [hi - lo for lo, hi in zip(b, b[1:])]
+    assert max(sizes) <= 15 and sizes[-3:] == [9, 3, 3] and sum(sizes) == 512
