@@ -59,7 +59,7 @@ WORKLOADS = {
                            "bf16 operands, three products per contraction)"),
 }
 # the other configurations carried by the one-GPU line: (workload, heads, steps)
-EXTRAS = (("cfg2", 64, 20), ("cfg3", 128, 8), ("cfg4", 4, 5), ("n8192", 32, 5), ("cfg1", 2, 20), ("f32-n2048", 64, 5))
+EXTRAS = (("cfg2", 64, 20), ("cfg3", 128, 8), ("cfg4", 32, 5), ("n8192", 32, 5), ("cfg1", 2, 20), ("f32-n2048", 64, 5))
 GEMM_UNITS = {"pass12": 5, "pass3": 9, "pass4": 8}
 EXEC_OVER_ALG = sum(GEMM_UNITS.values()) / 12.0
 # dram__bytes_read.sum + dram__bytes_write.sum per head of one launch of each pass at N_Q=4096,
@@ -508,7 +508,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true",
                     help="one GPU: skip the other configurations, the memory sweep and the Triton comparison")
     ap.add_argument("--no-competitor", action="store_true", help="skip only the reference's Triton operator")
-    ap.add_argument("--competitor-timeout", type=int, default=300)
+    ap.add_argument("--competitor-timeout", type=int, default=240)
     ap.add_argument("--competitor-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.competitor_child:

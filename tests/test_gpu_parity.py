@@ -478,6 +478,11 @@ def test_host_buffers_end_to_end():
             assert O.rel_err(g, r) < TOL_BF16, n
     finally:
         fhob.ops.HOST_RANGE_BYTES = saved
+    # the staging sets and workspaces the module keeps between calls can be given back
+    del got
+    before = torch.cuda.memory_allocated()
+    fhob.release_cached_memory()
+    assert torch.cuda.memory_allocated() < before and not fhob.ops._staging and not fhob.ops._workspaces
 
 
 def test_wrong_inputs_raise():
