@@ -31,6 +31,8 @@ def attention_backward(Q, K, V, O, dO, L, scale, *, is_causal: bool = False, sli
     Same maths as ``attn_bwd`` (jax_refs/flash_impl.py:124-173) with
     ``P = exp(S - L)`` and ``D = rowsum(dO * O)``; O(N) memory.
     """
+    if Q.numel() == 0 or K.numel() == 0 or V.numel() == 0:
+        return tuple(torch.zeros_like(t) for t in (Q, K, V))   # no queries or no keys: nothing to launch
     # the problem struct wants three cotangent tensors of the right shapes; they are not read
     prob = _Problem(Q, K, V, O, dO, Q, K, V, L, scale, is_causal, impl, need_outputs=False, window=sliding_window)
     dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=t.device) for t in (Q, K, V))   # contiguous results

@@ -224,6 +224,18 @@ def _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, check,
     return prob.outputs()
 
 
+def _empty_problem(Q, K, V, dO, out):
+    """An empty batch, no queries or no keys: nothing is launched.  Sums over no keys (or no
+    queries) are zero, so every result that has any element is zero - the same definition as for
+    queries without a visible key under a causal mask.  (The reference cannot launch such a
+    problem: its grids would have no blocks.)"""
+    if out is not None:
+        for t in out:
+            t.zero_()
+        return tuple(out)
+    return tuple(torch.zeros_like(t) for t in (Q, K, V, dO))
+
+
 def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = False,
                  sliding_window: Optional[int] = None, impl: str = "auto", check: Optional[bool] = None,
                  device: Optional[torch.device] = None, out=None, workspace=None) -> Tuple[torch.Tensor, ...]:
@@ -268,6 +280,8 @@ def flash_bwdbwd(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, *, is_causal: bool = F
     memory, and the four results come back as pinned host tensors (or in
     ``out``, four host tensors, preferably pinned) after a stream synchronise.
     """
+    if Q.numel() == 0 or K.numel() == 0 or V.numel() == 0:
+        return _empty_problem(Q, K, V, dO, out)
     if Q.device.type == "cuda":
         return _run_device(Q, K, V, O, dO, ddQ, ddK, ddV, L, scale, is_causal, impl, bool(check), sliding_window,
                            out, workspace)
@@ -443,6 +457,11 @@ def attention_forward(Q, K, V, scale=None, *, is_causal: bool = False, sliding_w
         raise ValueError(f"K {tuple(k.shape)} / V {tuple(v.shape)} do not match Q {tuple(q.shape)}")
     if scale is None:
         scale = d ** -0.5
+    if bh == 0 or n_q == 0 or k.shape[1] == 0 or d == 0 or d_v == 0:
+        # nothing to launch; without keys a query has O = 0 and L = -inf, like one the mask leaves without keys
+        o = torch.zeros(bh, n_q, d_v, dtype=Q.dtype, device=Q.device) if need_o else None
+        lse = torch.full((bh, n_q), float("-inf"), dtype=torch.float32, device=Q.device)
+        return (o.reshape(*shape_q[:-1], d_v) if need_o else None), lse.reshape(shape_q[:-1])
     o = torch.empty(bh, n_q, d_v, dtype=Q.dtype, device=Q.device) if need_o else None
     lse = torch.empty(bh, n_q, dtype=torch.float32, device=Q.device)
     p = _lib.FhobProblem()

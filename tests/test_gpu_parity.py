@@ -485,6 +485,22 @@ def test_host_buffers_end_to_end():
     assert torch.cuda.memory_allocated() < before and not fhob.ops._staging and not fhob.ops._workspaces
 
 
+def test_empty_problems_on_the_device():
+    """No keys: O = 0, L = -inf, every gradient zero; an empty batch: empty results.  Nothing is launched."""
+    import fhob
+    q = torch.randn(2, 16, 64, device="cuda", dtype=torch.bfloat16)
+    k, v = q[:, :0], q[:, :0, :32]
+    o, lse = fhob.attention_forward(q, k, v, 0.125)
+    assert o.shape == (2, 16, 32) and not o.any() and torch.isneginf(lse).all()
+    assert torch.isneginf(fhob.produce_L(q, k)).all()
+    got = fhob.flash_bwdbwd(q, k, v, o, o, q, k, v, lse, 0.125, check=True)
+    assert [tuple(t.shape) for t in got] == [(2, 16, 64), (2, 0, 64), (2, 0, 32), (2, 16, 32)]
+    assert not got[0].any() and not got[3].any()
+    e = q[:0]
+    assert fhob.attention_forward(e, e, e)[0].shape == (0, 16, 64)
+    assert all(t.numel() == 0 for t in fhob.flash_bwdbwd(e, e, e, e, e, e, e, e, e[:, :, 0].float(), 0.125))
+
+
 def test_wrong_inputs_raise():
     import fhob
     q = torch.zeros(2, 128, 64, device="cuda", dtype=torch.bfloat16)
