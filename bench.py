@@ -715,6 +715,29 @@ def main():
             host_out[1].copy_(x["k"], non_blocking=True)
         torch.cuda.synchronize()
         link["h2d_duplex"] = 2 * big.numel() * 2 / (u0.elapsed_time(u1) * 1e-3) / 1e9
+        if world > 1:
+            # all ranks upload at the same moment (the slowest rank counts): what the host gives
+            # every link when each GPU of the job pulls from it at once
+            barrier()
+            e0.record()
+            for _ in range(2):
+                dst.copy_(big, non_blocking=True)
+            e1.record()
+            torch.cuda.synchronize()
+            link["h2d_all_ranks"] = 2 * big.numel() * 2 / (max_over_ranks(e0.elapsed_time(e1)) * 1e-3) / 1e9
+            # the same with every rank also downloading (two parts up, one part down, like the step)
+            barrier()
+            up.wait_stream(torch.cuda.current_stream(dev))
+            down.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(up):
+                u0.record()
+                for _ in range(2):
+                    dst.copy_(big, non_blocking=True)
+                u1.record()
+            with torch.cuda.stream(down):
+                host_out[1].copy_(x["k"], non_blocking=True)
+            torch.cuda.synchronize()
+            link["h2d_all_ranks_duplex"] = 2 * big.numel() * 2 / (max_over_ranks(u0.elapsed_time(u1)) * 1e-3) / 1e9
         del dst
         def e2e_step():
             return fhob.flash_bwdbwd(*host, case.scale, is_causal=w["causal"], device=dev, out=host_out)
@@ -737,6 +760,9 @@ def main():
                    link_alone_h2d_gbs=round(link["h2d"], 1), link_alone_d2h_gbs=round(link["d2h"], 1),
                    frac_of_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d"], 3),
                    link_alone_h2d_gbs_per_input=link["h2d_per_tensor"],
+                   link_all_ranks_at_once_h2d_gbs=round(link["h2d_all_ranks"], 1) if "h2d_all_ranks" in link else None,
+                   link_all_ranks_at_once_duplex_h2d_gbs=(round(link["h2d_all_ranks_duplex"], 1)
+                                                          if "h2d_all_ranks_duplex" in link else None),
                    link_duplex_h2d_gbs=round(link["h2d_duplex"], 1),
                    frac_of_duplex_link_h2d=round(case.in_bytes / (ms_e2e * 1e-3) / 1e9 / link["h2d_duplex"], 3),
                    host_placement=placement)
