@@ -41,20 +41,3 @@ def test_reference_arm_prints_one_contract_line():
     assert j["cpu_baseline"]["value"] == j["value"] == j["e2e"]["value"] > 0
     assert j["e2e"]["h2d_bytes_per_step"] == 0 and j["e2e"]["d2h_bytes_per_step"] == 0
 
-
-def test_dram_traffic_constants_are_those_of_the_committed_capture():
-    """`roofline.traffic` scales the per-head DRAM bytes of the 16-head ncu capture; the constants in
-    bench.py have to be the figures of the summary that is committed, and the kernel names those of
-    the launch list."""
-    import re
-    text = (ROOT / "profiles" / "tc_pass_kernels_cfg5_16heads.md").read_text()
-    def row(label):
-        line = next(l for l in text.splitlines() if l.startswith(f"| {label}"))
-        return [float(x) for x in re.findall(r"([0-9]+\.[0-9]+) MB", line)]
-    reads, writes = row("dram__bytes_read.sum"), row("dram__bytes_write.sum")
-    assert len(reads) == len(writes) == 3
-    for stage, r, w_ in zip(("pass12", "pass3", "pass4"), reads, writes):
-        assert abs(bench.DRAM_BYTES_PER_HEAD[("cfg5", stage)] * 16 / 1e6 - (r + w_)) < 0.02, stage
-    launches = (ROOT / "profiles" / "launch_list_cfg5_512heads.md").read_text()
-    for stage in ("pass12", "pass3", "pass4"):
-        assert bench.KERNEL_NAMES[stage].format(d=128) in launches, stage
