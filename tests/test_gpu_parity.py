@@ -31,11 +31,11 @@ def _oracle(x64, scale, causal):
         dead = nq - nk
         live = {n: (t[:, dead:] if n in ("q", "do", "ddq") else t) for n, t in x64.items()}
         ref, lse, o, stats = _oracle(live, scale, causal)
-        z = torch.zeros_like(x64["q"][:, :dead])
-        ref = (torch.cat([z, ref[0]], 1), ref[1], ref[2], torch.cat([z, ref[3]], 1))
+        z, zv = torch.zeros_like(x64["q"][:, :dead]), torch.zeros_like(x64["do"][:, :dead])   # head dims d and d_v
+        ref = (torch.cat([z, ref[0]], 1), ref[1], ref[2], torch.cat([zv, ref[3]], 1))
         lse = torch.cat([torch.full((lse.shape[0], dead), -float("inf"), dtype=lse.dtype), lse], 1)
         stats = tuple(torch.cat([z[:, :, 0], t], 1) for t in stats)
-        return ref, lse, torch.cat([z, o], 1), stats
+        return ref, lse, torch.cat([zv, o], 1), stats
     vals = list(x64.values())
     ref = O.bwdbwd_closed_form(*vals, scale, causal)
     lse = O.attn_lse(x64["q"], x64["k"], scale, causal)
@@ -772,6 +772,57 @@ def test_random_shapes_all_tensor_core_kernels(bh, nq, nk, d, causal, window):
                             scale, check=True, **kw)
     for n, g, r in zip(OUT_NAMES, got, ref):
         assert O.rel_err(g, r) < TOL_BF16, n
+
+
+def _random_mixed_cases(n, seed):
+    """Random head dims (two of them), storage types, masks and lengths, including causal problems
+    with fewer keys than queries; fp32 cases keep both head dims at most 64 (the tensor-core path)."""
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < n:
+        dtype = rng.choice(["bf16", "bf16", "f16", "f32"])
+        top = 8 if dtype == "f32" else 16
+        d, dv = 8 * rng.randint(1, top), 8 * rng.randint(1, top)
+        nq, nk = rng.randint(1, 330), rng.randint(1, 330)
+        causal = rng.random() < 0.5
+        window = rng.choice([None, rng.randint(1, 200)]) if causal else None
+        cases.append((rng.randint(1, 3), nq, nk, d, dv, dtype, causal, window))
+    return cases
+
+
+@pytest.mark.parametrize("bh,nq,nk,d,dv,dtype,causal,window", _random_mixed_cases(48, seed=2025))
+def test_random_head_dims_types_and_masks_on_the_tensor_cores(bh, nq, nk, d, dv, dtype, causal, window):
+    import fhob
+    tdt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[dtype]
+    tol = TOL_F32 if dtype == "f32" else TOL_BF16
+    g = torch.Generator().manual_seed(nq * 1000 + nk + d)
+    mk = lambda n, dd: torch.randn(bh, n, dd, generator=g, dtype=torch.float64).to(tdt).double()
+    x = dict(q=mk(nq, d), k=mk(nk, d), v=mk(nk, dv), do=mk(nq, dv), ddq=mk(nq, d), ddk=mk(nk, d), ddv=mk(nk, dv))
+    scale = d ** -0.5
+    ref, lse_ref, o_ref, _ = _oracle(x, scale, causal) if window is None else (None, None, None, None)
+    if window is not None:
+        import math
+        dead = nq - nk if nk < nq else 0          # queries without any visible key: evaluate the oracle on the rest
+        live = {n: (t[:, dead:] if n in ("q", "do", "ddq") else t) for n, t in x.items()}
+        r = O.bwdbwd_closed_form(*live.values(), scale, causal, sliding_window_length=window)
+        z = torch.zeros_like(x["q"][:, :dead]), torch.zeros_like(x["do"][:, :dead])
+        ref = (torch.cat([z[0], r[0]], 1), r[1], r[2], torch.cat([z[1], r[3]], 1))
+    dev = {n: t.to(tdt).cuda() for n, t in x.items()}
+    kw = dict(is_causal=causal, sliding_window=window, impl="tcgen05")
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **kw)
+    if window is None:
+        live_rows = slice(max(0, nq - nk) if causal else 0, None)
+        assert O.rel_err(o[:, live_rows], o_ref[:, live_rows]) < tol
+        assert O.rel_err(lse[:, live_rows], lse_ref[:, live_rows]) < 1e-4
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o, dev["do"], dev["ddq"], dev["ddk"], dev["ddv"], lse,
+                            scale, check=True, **kw)
+    for n, a, r in zip(OUT_NAMES, got, ref):
+        assert torch.isfinite(a).all(), n
+        # against the tensor's abs-max, or against 1e-3 where the exact result vanishes (a query row
+        # with a single visible key has no second-order terms: the kernels then return rounding noise)
+        err = float((a.double().cpu() - r).abs().max() / max(float(r.abs().max()), 1e-3)) if r.numel() else 0.0
+        assert err < tol, (n, err)
 
 
 def test_expired_wait_is_reported_and_leaves_the_context_usable():
