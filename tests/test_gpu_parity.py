@@ -825,6 +825,53 @@ def test_random_head_dims_types_and_masks_on_the_tensor_cores(bh, nq, nk, d, dv,
         assert err < tol, (n, err)
 
 
+def _random_simt_cases(n, seed):
+    import random
+    rng = random.Random(seed)
+    cases = []
+    while len(cases) < n:
+        dtype = rng.choice(["f32", "f32", "bf16"])
+        step = 4 if dtype == "f32" else 8           # rows stay 16-byte aligned
+        d, dv = step * rng.randint(1, 128 // step), step * rng.randint(1, 128 // step)
+        nq, nk = rng.randint(1, 200), rng.randint(1, 200)
+        causal = rng.random() < 0.5
+        window = rng.choice([None, rng.randint(1, 150)]) if causal else None
+        cases.append((rng.randint(1, 3), nq, nk, d, dv, dtype, causal, window))
+    return cases
+
+
+@pytest.mark.parametrize("bh,nq,nk,d,dv,dtype,causal,window", _random_simt_cases(24, seed=2026))
+def test_random_head_dims_types_and_masks_on_the_cuda_cores(bh, nq, nk, d, dv, dtype, causal, window):
+    """The CUDA-core kernels (operator, forward, first backward) on random problems: any head dims up
+    to 128 that keep rows 16-byte aligned, two of them, both storage classes, every mask."""
+    import fhob
+    import math
+    tdt = {"bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+    tol = TOL_F32 if dtype == "f32" else TOL_BF16
+    g = torch.Generator().manual_seed(nq * 1000 + nk + d)
+    mk = lambda n, dd: torch.randn(bh, n, dd, generator=g, dtype=torch.float64).to(tdt).double()
+    x = dict(q=mk(nq, d), k=mk(nk, d), v=mk(nk, dv), do=mk(nq, dv), ddq=mk(nq, d), ddk=mk(nk, d), ddv=mk(nk, dv))
+    scale = d ** -0.5
+    w = math.inf if window is None else window
+    dead = nq - nk if (causal and nk < nq) else 0   # queries without any visible key: oracle on the rest
+    live = {n: (t[:, dead:] if n in ("q", "do", "ddq") else t) for n, t in x.items()}
+    r = O.bwdbwd_closed_form(*live.values(), scale, causal, sliding_window_length=w)
+    first = O.attn_bwd(live["q"], live["k"], live["v"], live["do"], scale, causal, sliding_window_length=w)
+    zq, zv = torch.zeros_like(x["q"][:, :dead]), torch.zeros_like(x["do"][:, :dead])
+    ref = (torch.cat([zq, r[0]], 1), r[1], r[2], torch.cat([zv, r[3]], 1))
+    first_ref = (torch.cat([zq, first[0]], 1), first[1], first[2])
+    dev = {n: t.to(tdt).cuda() for n, t in x.items()}
+    kw = dict(is_causal=causal, sliding_window=window, impl="simt")
+    o, lse = fhob.attention_forward(dev["q"], dev["k"], dev["v"], scale, **kw)
+    got_first = fhob.attention_backward(dev["q"], dev["k"], dev["v"], o, dev["do"], lse, scale, **kw)
+    got = fhob.flash_bwdbwd(dev["q"], dev["k"], dev["v"], o, dev["do"], dev["ddq"], dev["ddk"], dev["ddv"], lse,
+                            scale, check=True, **kw)
+    for n, a, rr in list(zip(("dq", "dk", "dv"), got_first, first_ref)) + list(zip(OUT_NAMES, got, ref)):
+        assert torch.isfinite(a).all(), n
+        err = float((a.double().cpu() - rr).abs().max() / max(float(rr.abs().max()), 1e-3)) if rr.numel() else 0.0
+        assert err < tol, (n, err)
+
+
 def test_expired_wait_is_reported_and_leaves_the_context_usable():
     """A device wait that can never complete gives up after about a second, sets FHOB_ERR_TIMEOUT
     in the status word and the kernel returns; the next operator call clears the word and works."""
