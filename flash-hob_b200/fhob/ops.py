@@ -373,8 +373,9 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
         # a previous call may still be using the set on other streams
         st["read"] = st["drained"] = None
     up.wait_stream(down)
-    # the pre-pass of every range clears the status word, so each range's word is kept
-    status_host = torch.zeros(n_chunks, dtype=torch.int32, pin_memory=True) if check else None
+    # the pre-pass of every range clears the status word, so each range's word is kept (on the device:
+    # a small device-to-host copy per range would queue behind the downloads on the copy engine)
+    status_dev = torch.zeros(n_chunks, dtype=torch.int32, device=dev) if check else None
     for i, (lo, hi) in enumerate(zip(bounds, bounds[1:])):
         st, n = ring[i % len(ring)], hi - lo
         with torch.cuda.stream(up):
@@ -391,7 +392,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
         res = _run_device(*(None if t is None else t[:n] for t in st["ins"]), scale, is_causal, impl, False, window,
                           out=tuple(t[:n] for t in st["res"]), workspace=ws)
         if check:
-            status_host[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
+            status_dev[i:i + 1].copy_(ws[:4].view(torch.int32), non_blocking=True)
         st["read"] = torch.cuda.Event()
         st["read"].record(main)
         down.wait_event(st["read"])
@@ -403,7 +404,7 @@ def _run_host(mats, L, scale, is_causal, impl, check, dev, window=None, out=None
     down.synchronize()
     if check:
         main.synchronize()
-        for status in status_host.tolist():
+        for status in status_dev.tolist():
             _lib.check(status, "fhob_bwdbwd (device status)")
     return tuple(t.reshape(s) for t, s in zip(outs_host, out_shapes))
 
